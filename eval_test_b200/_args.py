@@ -1,0 +1,47 @@
+"""Argument checks shared by the ``custom_kernel`` shims: the kernels take raw pointers, so the shims verify
+that the tensors really have the reference's layouts before handing the pointers over."""
+from __future__ import annotations
+
+import torch
+
+from . import formats as F
+
+
+def _strides_match(t: torch.Tensor, want: tuple[int, ...]) -> bool:
+    return all(s == w for s, w, n in zip(t.stride(), want, t.shape) if n > 1)
+
+
+def operand_ptr(t: torch.Tensor, rows: int, k2: int, L: int, name: str) -> int:
+    """``[rows, K/2, L]`` packed e2m1, K-major rows, batch outermost in memory."""
+    if t.dim() != 3 or tuple(t.shape) != (rows, k2, L):
+        raise ValueError(f"{name}: expected shape {(rows, k2, L)}, got {tuple(t.shape)}")
+    if t.element_size() != 1:
+        raise ValueError(f"{name}: expected a 1-byte packed fp4 dtype, got {t.dtype}")
+    if not t.is_cuda:
+        raise ValueError(f"{name}: must be a CUDA tensor")
+    if not _strides_match(t, (k2, 1, rows * k2)):
+        raise ValueError(f"{name}: expected strides {(k2, 1, rows * k2)}, got {t.stride()}")
+    return t.data_ptr()
+
+
+def scales_ptr(t: torch.Tensor, rows: int, K: int, L: int, name: str) -> int:
+    """The 6-D swizzled view ``[32, 4, R, 4, Kb, L]`` with the canonical strides."""
+    R, Kb = F.ceil_div(rows, 128), F.ceil_div(K // F.SF_VEC, 4)
+    if tuple(t.shape) != (32, 4, R, 4, Kb, L) or t.element_size() != 1 or not t.is_cuda:
+        raise ValueError(f"{name}: expected a CUDA 1-byte tensor of shape {(32, 4, R, 4, Kb, L)}, "
+                         f"got {tuple(t.shape)} {t.dtype} {t.device}")
+    if not _strides_match(t, F.permuted_strides(rows, K)):
+        raise ValueError(f"{name}: expected strides {F.permuted_strides(rows, K)}, got {t.stride()}")
+    return t.data_ptr()
+
+
+def output_ptr(c: torch.Tensor, M: int, N: int, L: int, name: str = "c") -> int:
+    if tuple(c.shape) != (M, N, L) or c.dtype != torch.float16 or not c.is_cuda:
+        raise ValueError(f"{name}: expected CUDA float16 {(M, N, L)}, got {tuple(c.shape)} {c.dtype} {c.device}")
+    if not _strides_match(c, (N, 1, M * N)):
+        raise ValueError(f"{name}: expected strides {(N, 1, M * N)}, got {c.stride()}")
+    return c.data_ptr()
+
+
+def stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream

@@ -1,0 +1,18 @@
+// Host-side helpers shared by the translation units of the library (not part of the C ABI).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/nvfp4_b200.h"
+
+namespace nvfp4 {
+
+// Number of SMs of a device (cached).
+int sm_count(int dev);
+// Device-visible status word of a device (mapped pinned host memory, allocated on first use).
+// A kernel whose bounded wait expires stores a DeviceStatus code there; nullptr if allocation failed.
+int* status_word(int dev);
+// Budget, in nanoseconds, after which a device-side wait gives up (NVFP4_WAIT_BUDGET_MS, default 2000 ms).
+unsigned long long wait_budget_ns();
+
+}  // namespace nvfp4

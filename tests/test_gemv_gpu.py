@@ -1,0 +1,111 @@
+"""GPU parity of nvfp4_gemv (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from _util import operand_np, out_np, scales_np, to_device
+
+pytestmark = pytest.mark.gpu
+
+# shapes of the harness's GEMV correctness list (m, k, l)
+REFERENCE_TESTS = [(128, 256, 1), (128, 1536, 1), (128, 3072, 1), (256, 7168, 1), (2432, 4608, 2),
+                   (384, 7168, 2), (512, 512, 2), (512, 4096, 2), (512, 1536, 2)]
+
+
+def _run(data, alpha=1.0):
+    from eval_test_b200 import _lib, nvfp4_gemv
+    out = nvfp4_gemv.custom_kernel(data, alpha=alpha) if alpha != 1.0 else nvfp4_gemv.custom_kernel(data)
+    torch.cuda.synchronize()
+    assert _lib.device_status(torch.cuda.current_device()) == 0
+    assert out is data[-1]
+    return out_np(out)[:, :, 0]
+
+
+def _oracle(oracle, data, alpha=1.0):
+    a, b, _, _, sfa_p, sfb_p, _ = data
+    return oracle.c_gemv(operand_np(a), operand_np(b), scales_np(sfa_p), scales_np(sfb_p), alpha)
+
+
+@pytest.mark.parametrize("m,k,l", REFERENCE_TESTS)
+def test_reference_style_bit_exact(oracle, m, k, l):
+    from eval_test_b200 import inputs
+    data = to_device(inputs.gemv_reference_style(m, k, l, seed=1111, device="cpu"))
+    got, want = _run(data), _oracle(oracle, data)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("m,k,l", [(128, 256, 1), (384, 2048 + 64, 3), (200, 1024, 2), (4096, 7168, 2)])
+def test_quantized_within_tolerance(oracle, m, k, l):
+    """N(0,1) data: fp32 summation order differs from the oracle, so compare with the harness's
+    rtol = atol = 1e-3 rule and the 1e-2 * max|ref| bound."""
+    from eval_test_b200 import check, inputs
+    data = to_device(inputs.gemv_quantized(m, k, l, seed=3, device="cpu"))
+    got, want = torch.from_numpy(_run(data, alpha=0.5)), torch.from_numpy(_oracle(oracle, data, alpha=0.5))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
+def test_all_bit_patterns(oracle):
+    """Every byte value (all 16 x 16 nibble pairs, negative zeros included) in A and in x."""
+    from eval_test_b200 import inputs
+    data = list(inputs.gemm_reference_style(256, 128, 1024, 2, seed=5, device="cpu"))
+    data[-1] = torch.empty((2, 256, 1), dtype=torch.float16).permute(1, 2, 0)  # [m, 1, l] output
+    data = to_device(tuple(data))
+    got, want = _run(data), _oracle(oracle, data)
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_linearity_full_size():
+    """Size-independent property at the full benchmark shape: doubling alpha doubles every output exactly
+    (power-of-two scaling commutes with the fp16 rounding while no value is subnormal or overflows)."""
+    from eval_test_b200 import inputs, nvfp4_gemv
+    data = inputs.gemv_quantized(16384, 16384, 4, seed=0, device="cuda")
+    c1 = nvfp4_gemv.custom_kernel(data, alpha=1.0).clone()
+    c2 = nvfp4_gemv.custom_kernel(data, alpha=2.0).clone()
+    torch.cuda.synchronize()
+    ok = (c1.float().abs() > 1e-3) & (c1.float().abs() < 3e4)
+    assert ok.float().mean() > 0.9
+    assert torch.equal((2 * c1.float())[ok], c2.float()[ok])
+
+
+def test_full_size_rows_against_oracle(oracle):
+    """Full benchmark shape; a sample of rows is checked against the oracle (the whole matrix would take the
+    CPU too long inside the test budget)."""
+    from eval_test_b200 import check, inputs, nvfp4_gemv
+    m = k = 16384
+    data = inputs.gemv_quantized(m, k, 4, seed=0, device="cuda")
+    a, b, _, _, sfa_p, sfb_p, c = data
+    nvfp4_gemv.custom_kernel(data)
+    torch.cuda.synchronize()
+    rows = slice(128 * 37, 128 * 39)  # two whole 128-row blocks
+    a_np = operand_np(a)[:, rows]
+    sf = scales_np(sfa_p).reshape(4, m // 128, -1)[:, 37:39].reshape(-1)
+    want = torch.from_numpy(oracle.c_gemv(a_np, operand_np(b), sf, scales_np(sfb_p)))
+    got = torch.from_numpy(out_np(c)[:, rows, 0])
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+
+
+def test_bad_arguments_are_rejected():
+    from eval_test_b200 import _lib
+    lib = _lib.load()
+    buf = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda")
+    p = buf.data_ptr()
+    assert lib.nvfp4_gemv(p, p, p, p, p, 128, 100, 1, 128, 1.0, None) == -3   # K % 64
+    assert lib.nvfp4_gemv(p, p, p, p, p, 0, 256, 1, 128, 1.0, None) == -2     # M <= 0
+    assert lib.nvfp4_gemv(None, p, p, p, p, 128, 256, 1, 128, 1.0, None) == -1
+    assert lib.nvfp4_gemv(p + 4, p, p, p, p, 128, 256, 1, 128, 1.0, None) == -5
+    assert "K" in _lib.strerror(-3)
+
+
+def test_wait_selftest_expires_and_reports():
+    """A wait that nothing satisfies returns an error status instead of hanging; the context stays usable."""
+    import ctypes
+    from eval_test_b200 import _lib
+    lib = _lib.load()
+    _lib.device_status(torch.cuda.current_device())
+    ms = ctypes.c_double(0)
+    assert lib.nvfp4_wait_selftest(50, ctypes.byref(ms), None) == 0
+    assert 40 <= ms.value < 500
+    assert _lib.device_status(torch.cuda.current_device()) == 105
+    assert _lib.device_status(torch.cuda.current_device()) == 0
+    assert float(torch.ones(4, device="cuda").sum()) == 4.0
