@@ -300,16 +300,17 @@ def main():
         res = wl.run(e2e_data)
         host_out.copy_(flat(res), non_blocking=True)
 
-    for _ in range(2):
+    e2e_steps = 1 if args.small else args.e2e_steps
+    for _ in range(0 if args.small else 2):
         e2e_step()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
-    for _ in range(args.e2e_steps):
+    for _ in range(e2e_steps):
         e2e_step()
     e1.record(stream)
     barrier()
-    e2e_ms = e0.elapsed_time(e1) / args.e2e_steps
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # ---- max over ranks ----
     t = torch.tensor([total_ms, kern_ms, e2e_ms], device=dev, dtype=torch.float64)
@@ -332,7 +333,7 @@ def main():
                          "bytes_per_launch": step_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
             "e2e": {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": wl.unit,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
-                    "steps": args.e2e_steps},
+                    "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks.summary(),
         }
         traffic = ROOT / "profiles" / "traffic.json"
@@ -341,7 +342,7 @@ def main():
                 line["roofline"]["traffic"] = json.loads(traffic.read_text()).get(wl.name)
             except Exception:
                 pass
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and not args.small:
             line["cpu_baseline"] = cpu_baseline(wl, data)
         print(json.dumps(line), flush=True)
 

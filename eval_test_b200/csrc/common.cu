@@ -1,6 +1,7 @@
 // Per-device state of the library (SM count, status word), error strings, and a self-test of the
 // bounded-wait mechanism that every kernel's pipeline relies on.
 #include <cuda_runtime.h>
+#include <cudaTypedefs.h>
 #include <stdlib.h>
 
 #include <mutex>
@@ -57,6 +58,26 @@ unsigned long long wait_budget_ns() {
         return (unsigned long long)ms * 1000000ull;
     }();
     return v;
+}
+
+int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+                 const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle) {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void* f = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            f = nullptr;
+        return (PFN_cuTensorMapEncodeTiled_v12000)f;
+    }();
+    if (!fn || rank < 1 || rank > 5) return NVFP4_ERR_TENSORMAP;
+    cuuint64_t d[5], s[4];
+    cuuint32_t b[5], es[5] = {1, 1, 1, 1, 1};
+    for (int i = 0; i < rank; i++) { d[i] = dims[i]; b[i] = box[i]; }
+    for (int i = 0; i + 1 < rank; i++) s[i] = strides[i];
+    CUresult r = fn(map, dtype, (cuuint32_t)rank, const_cast<void*>(base), d, s, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? NVFP4_OK : NVFP4_ERR_TENSORMAP;
 }
 
 // One thread waits on an mbarrier that nothing ever arrives on: the wait must expire within the

@@ -8,8 +8,13 @@
 // Work unit = 32 rows of one 128-row block of one batch: rows {128*rb + 32*g + 8*j + i : g<4, i<8}.
 // That row set is chosen because its scale factors form one contiguous 128-byte slice of every
 // 512-byte atom of the swizzled scale layout, so scales stream with full sector use.
-// A persistent CTA walks its units; one producer warp feeds a shared-memory ring with 1-D bulk
-// copies (row segments of A, 128-byte scale slices), consumer warps decode and accumulate:
+// A persistent CTA walks its units; a producer feeds a shared-memory ring, consumer warps decode and
+// accumulate.  The ring is filled by two tiled TMA loads per stage when M is a multiple of 128 - a
+// 5-D view of A (k, row-in-8, j, g, row-block) brings the unit's 32 row segments in one instruction,
+// a 4-D view of the scales brings its 128-byte slices of consecutive atoms (128-byte swizzle, which
+// also spreads the consumers' reads over the banks); measured on B200, per-row 1-D bulk copies cost
+// about 32 ns each per SM whatever their size and cap the kernel far below HBM speed, so they are
+// kept only for ragged M.  Consumers:
 //   * e2m1 -> int8 (2*value) with one byte-permute per 4 elements: the permute's selector nibble
 //     is the e2m1 nibble itself, its 3 low bits index an 8-entry table held in two registers, and
 //     its top bit (the sign) makes the permute return 0, so "positives" and (after flipping the
@@ -20,6 +25,8 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <string.h>
 
 #include "nvfp4_internal.h"
 #include "ptx_sm100.cuh"
@@ -38,7 +45,7 @@ struct GemvParams {
     unsigned long long budget_ns;
 };
 
-constexpr int SF_SLOT = 144;  // 128-byte scale slice + 16 bytes of padding (spreads shared-memory banks)
+constexpr int SF_SLOT = 144;  // ragged-M path: 128-byte scale slice + 16 bytes of padding (spreads banks)
 
 __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
@@ -63,13 +70,24 @@ __device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
     return __half22float2(*reinterpret_cast<__half2*>(&h));
 }
 
-template <int CW, int KC, int STAGES>
-__global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams p) {
+template <int KC, bool TILED>
+struct GemvStage {
+    static constexpr int A_BYTES = 32 * (KC / 2);
+    static constexpr int SF_BYTES = (KC / 64) * (TILED ? 128 : SF_SLOT);
+    static constexpr int BYTES = (A_BYTES + SF_BYTES + 1023) / 1024 * 1024;  // scales first, then A
+    static constexpr int A_OFF = (SF_BYTES + 127) / 128 * 128;
+};
+
+// TILED: tiled TMA loads (needs M % 128 == 0); otherwise per-row bulk copies.
+// MODE 1 skips the arithmetic (measures the copy pipeline alone; tuning aid).
+template <int CW, int KC, int STAGES, int MINB, int MODE, bool TILED>
+__global__ void __launch_bounds__((CW + 1) * 32, MINB)
+gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_sf,
+            const GemvParams p) {
+    using St = GemvStage<KC, TILED>;
     constexpr int RPW = 32 / CW;                 // rows per consumer warp
-    constexpr int A_STAGE = 32 * (KC / 2);       // bytes
-    constexpr int SF_STAGE = (KC / 64) * SF_SLOT;
-    constexpr int STAGE = A_STAGE + SF_STAGE;
-    static_assert(32 % CW == 0 && KC % 1024 == 0 && STAGE % 16 == 0, "bad tile");
+    constexpr int STAGE = St::BYTES;
+    static_assert(32 % CW == 0 && KC % 1024 == 0, "bad tile");
 
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 2];
@@ -78,7 +96,8 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
     const int kbs = K / 16;
     uint8_t* xs = smem;                                   // K int8: 2*x
     float* sxs = reinterpret_cast<float*>(smem + K);      // K/16 floats: 0.25 * sfx
-    uint8_t* ring = smem + K + kbs * 4;                   // K % 64 == 0 keeps this 16-byte aligned
+    // ring: 1024-byte aligned (the swizzled scale slices need it)
+    uint8_t* ring = smem + (((smem_u32(smem) + K + kbs * 4 + 1023u) & ~1023u) - smem_u32(smem));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
@@ -126,15 +145,24 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                     break;
                 }
                 const int k0 = c * KC;
-                const int kc = min(KC, K - k0);
-                const int nq = (kc + 63) / 64;
                 const uint32_t full = full0 + 8 * slot;
                 const uint32_t sbase = smem_u32(ring + (size_t)slot * STAGE);
-                if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(nvalid * (kc / 2) + nq * 128));
-                __syncwarp();
-                if (row < M) bulk_g2s(sbase + lane * (KC / 2), arow + k0 / 2, (uint32_t)(kc / 2), full);
-                for (int q = lane; q < nq; q += 32)
-                    bulk_g2s(sbase + A_STAGE + q * SF_SLOT, sfsrc + (size_t)(k0 / 64 + q) * 512, 128u, full);
+                if (TILED) {
+                    // out-of-range k (last chunk) is zero-filled and still counted, so the byte count is fixed
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(full, (uint32_t)(St::A_BYTES + St::SF_BYTES));
+                        tma_load_4d(sbase, &tmap_sf, 0, j, k0 / 64, l * RB + rb, full);
+                        tma_load_5d(sbase + St::A_OFF, &tmap_a, k0 / 16, 0, j, 0, l * RB + rb, full);
+                    }
+                } else {
+                    const int kc = min(KC, K - k0);
+                    const int nq = (kc + 63) / 64;
+                    if (lane == 0) mbar_arrive_expect_tx(full, (uint32_t)(nvalid * (kc / 2) + nq * 128));
+                    __syncwarp();
+                    if (row < M) bulk_g2s(sbase + St::A_OFF + lane * (KC / 2), arow + k0 / 2, (uint32_t)(kc / 2), full);
+                    for (int q = lane; q < nq; q += 32)
+                        bulk_g2s(sbase + q * SF_SLOT, sfsrc + (size_t)(k0 / 64 + q) * 512, 128u, full);
+                }
             }
         }
     } else {
@@ -194,12 +222,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                 }
                 const int k0 = c * KC;
                 const int kc = min(KC, K - k0);
-                const uint8_t* As = ring + (size_t)slot * STAGE;
-                const uint8_t* Ss = As + A_STAGE;
+                const uint8_t* Ss = ring + (size_t)slot * STAGE;
+                const uint8_t* As = Ss + St::A_OFF;
 #pragma unroll
                 for (int sub = 0; sub < KC / 1024; sub++) {
                     const int seg = sub * 32 + lane;  // 32-element segment of this chunk
-                    if (seg * 32 < kc) {
+                    if (MODE == 0 && seg * 32 < kc) {
                         const int kg = k0 + seg * 32;
                         const uint4 xa = *reinterpret_cast<const uint4*>(xs + kg);
                         const uint4 xb = *reinterpret_cast<const uint4*>(xs + kg + 16);
@@ -208,8 +236,12 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
                         for (int rr = 0; rr < RPW; rr++) {
                             const int ur = warp * RPW + rr;  // unit row = 8*g + i
                             const uint4 av = *reinterpret_cast<const uint4*>(As + ur * (KC / 2) + seg * 16);
-                            const uint16_t sfw = *reinterpret_cast<const uint16_t*>(
-                                Ss + (seg >> 1) * SF_SLOT + (((ur & 7) << 2) + (ur >> 3)) * 4 + (seg & 1) * 2);
+                            // scale slice of 64-element group q = seg/2: 16-byte chunk i, word g, bytes kb%4;
+                            // the tiled path stores 128-byte rows with chunk index XOR (q % 8)
+                            const int q = seg >> 1;
+                            const int sfoff = TILED ? q * 128 + ((((ur & 7) ^ (q & 7)) << 4) | ((ur >> 3) << 2))
+                                                    : q * SF_SLOT + (((ur & 7) << 4) | ((ur >> 3) << 2));
+                            const uint16_t sfw = *reinterpret_cast<const uint16_t*>(Ss + sfoff + (seg & 1) * 2);
                             const float2 sa = e4m3x2_to_float2(sfw);
                             int p0 = 0, n0 = 0, p1 = 0, n1 = 0;
                             dot8(av.x, xa.x, xa.y, p0, n0);
@@ -239,25 +271,57 @@ __global__ void __launch_bounds__((CW + 1) * 32, 1) gemv_kernel(const GemvParams
     __syncthreads();
 }
 
-template <int CW, int KC, int STAGES>
+template <int CW, int KC, int STAGES, int MINB = 1, int MODE = 0>
 static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
-    constexpr int STAGE = 32 * (KC / 2) + (KC / 64) * SF_SLOT;
-    const size_t smem = (size_t)p.K + (size_t)(p.K / 16) * 4 + (size_t)STAGES * STAGE;
-    auto kern = gemv_kernel<CW, KC, STAGES>;
-    static size_t configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
-    if (smem > 227 * 1024 - 256 || dev >= 64) return NVFP4_ERR_UNSUPPORTED;
-    if (configured[dev] < smem) {
-        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        configured[dev] = smem;
-    }
+    if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
+    const bool tiled = (p.M % 128 == 0);
+    const int stage = tiled ? GemvStage<KC, true>::BYTES : GemvStage<KC, false>::BYTES;
+    const size_t smem = (size_t)p.K + (size_t)(p.K / 16) * 4 + 1024 + (size_t)STAGES * stage;
+    if (smem > 227 * 1024 - 256) return NVFP4_ERR_UNSUPPORTED;
     const int RB = (p.M + 127) / 128;
+    const int Kb4 = (p.K / 16 + 3) / 4;
     const int units = p.L * RB * 4;
-    const int grid = units < sm_count(dev) ? units : sm_count(dev);
-    kern<<<grid, (CW + 1) * 32, smem, stream>>>(p);
+    const int slots = sm_count(dev) * MINB;
+    const int grid = units < slots ? units : slots;
+    CUtensorMap ta, tsf;
+    memset(&ta, 0, sizeof(ta));
+    memset(&tsf, 0, sizeof(tsf));
+    if (tiled) {
+        // A as 8-byte elements: (k, row within 8, j, g, batch*row-block); one box = the unit's 32 rows x KC/2 bytes
+        const uint64_t rowb = (uint64_t)(p.K / 2);
+        const uint64_t ad[5] = {(uint64_t)(p.K / 16), 8, 4, 4, (uint64_t)p.L * RB};
+        const uint64_t as[4] = {rowb, 8 * rowb, 32 * rowb, 128 * rowb};
+        const uint32_t ab[5] = {(uint32_t)(KC / 16), 8, 1, 4, 1};
+        int rc = encode_tiled(&ta, CU_TENSOR_MAP_DATA_TYPE_INT64, 5, p.a, ad, as, ab, CU_TENSOR_MAP_SWIZZLE_NONE);
+        if (rc) return rc;
+        // scales as bytes: (byte within a 128-byte slice, j, 64-element group, batch*row-block)
+        const uint64_t sd[4] = {128, 4, (uint64_t)Kb4, (uint64_t)p.L * RB};
+        const uint64_t ss[3] = {128, 512, (uint64_t)Kb4 * 512};
+        const uint32_t sb[4] = {128, 1, (uint32_t)(KC / 64), 1};
+        rc = encode_tiled(&tsf, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, p.sfa, sd, ss, sb, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (rc) return rc;
+    }
+    static size_t configured[64][2] = {};
+    if (tiled) {
+        auto kern = gemv_kernel<CW, KC, STAGES, MINB, MODE, true>;
+        if (configured[dev][1] < smem) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured[dev][1] = smem;
+        }
+        kern<<<grid, (CW + 1) * 32, smem, stream>>>(ta, tsf, p);
+    } else {
+        auto kern = gemv_kernel<CW, KC, STAGES, MINB, MODE, false>;
+        if (configured[dev][0] < smem) {
+            e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured[dev][0] = smem;
+        }
+        kern<<<grid, (CW + 1) * 32, smem, stream>>>(ta, tsf, p);
+    }
     e = cudaGetLastError();
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
@@ -283,6 +347,18 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
     p.status = status_word(dev);
     p.budget_ns = wait_budget_ns();
     cudaStream_t s = (cudaStream_t)stream;
-    if (K <= 32768) return launch_gemv<8, 2048, 5>(p, s);
-    return launch_gemv<8, 2048, 3>(p, s);
+    static const int variant = [] { const char* e = getenv("NVFP4_GEMV_VARIANT"); return e ? atoi(e) : 0; }();
+    if (K > 32768) return launch_gemv<8, 2048, 3>(p, s);
+    switch (variant) {  // tuning knob; 0 is the shipped configuration
+        case 1: return launch_gemv<16, 2048, 5>(p, s);
+        case 2: return launch_gemv<8, 4096, 2>(p, s);
+        case 3: return launch_gemv<8, 1024, 4, 2>(p, s);
+        case 4: return launch_gemv<16, 1024, 8>(p, s);
+        case 5: return launch_gemv<8, 1024, 8>(p, s);
+        case 6: return launch_gemv<8, 2048, 5, 1, 1>(p, s);   // no arithmetic: copy pipeline alone
+        case 7: return launch_gemv<8, 4096, 2, 1, 1>(p, s);
+        case 8: return launch_gemv<8, 1024, 4, 2, 1>(p, s);
+        case 9: return launch_gemv<16, 4096, 2>(p, s);
+        default: return launch_gemv<8, 2048, 5>(p, s);
+    }
 }

@@ -1,5 +1,6 @@
 // Host-side helpers shared by the translation units of the library (not part of the C ABI).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -14,5 +15,10 @@ int sm_count(int dev);
 int* status_word(int dev);
 // Budget, in nanoseconds, after which a device-side wait gives up (NVFP4_WAIT_BUDGET_MS, default 2000 ms).
 unsigned long long wait_budget_ns();
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (the library does not link libcuda).
+// dims / box in elements (innermost first), strides in bytes for dimensions 1..rank-1.
+int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
+                 const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle);
 
 }  // namespace nvfp4

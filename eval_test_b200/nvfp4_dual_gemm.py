@@ -1,0 +1,31 @@
+"""Drop-in for the reference's dual-GEMM entry point (eval/nvfp4_dual_gemm/submission.py:894-957).
+
+``custom_kernel(data)`` takes the 10-tuple of eval/nvfp4_dual_gemm/reference.py:48-73 -
+``(a, b1, b2, sfa, sfb1, sfb2, sfa_permuted, sfb1_permuted, sfb2_permuted, c)`` - and writes
+``c = fp16(silu(a @ b1^T) * (a @ b2^T))`` (block-scaled products, fp32 accumulation, the gating in fp32, one
+rounding) in place on the current stream.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _args, _lib
+
+
+def compile_kernel():
+    return _lib.load()
+
+
+def custom_kernel(data, alpha: float = 1.0):
+    a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, c = data
+    m, k2, l = a.shape
+    n = b1.shape[0]
+    k = 2 * k2
+    with torch.cuda.device(a.device):
+        code = _lib.load().nvfp4_dual_gemm(
+            _args.operand_ptr(a, m, k2, l, "a"), _args.operand_ptr(b1, n, k2, l, "b1"),
+            _args.operand_ptr(b2, n, k2, l, "b2"), _args.scales_ptr(sfa_p, m, k, l, "sfa_permuted"),
+            _args.scales_ptr(sfb1_p, n, k, l, "sfb1_permuted"), _args.scales_ptr(sfb2_p, n, k, l, "sfb2_permuted"),
+            _args.output_ptr(c, m, n, l), m, n, k, l, float(alpha), _args.stream_ptr(a.device))
+    _lib.check(code, "nvfp4_dual_gemm")
+    return c

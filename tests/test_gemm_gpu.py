@@ -1,0 +1,117 @@
+"""GPU parity of nvfp4_gemm / nvfp4_dual_gemm (through the C ABI) against the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from _util import dual_oracle_args, gemm_oracle_args, out_np, to_device
+
+pytestmark = pytest.mark.gpu
+
+# the harness's GEMM correctness list (m, n, k, l); the largest one is left to test_large_* below
+GEMM_TESTS = [(128, 256, 256, 1), (128, 1536, 7168, 1), (128, 3072, 1536, 1), (256, 7168, 256, 1),
+              (256, 7168, 2048, 1), (384, 7168, 2304, 1), (512, 512, 7168, 1), (512, 4096, 512, 1),
+              (512, 1536, 7168, 1)]
+DUAL_TESTS = [(256, 512, 256, 1), (1536, 512, 7168, 1), (3072, 1024, 1536, 1), (7168, 1024, 256, 1),
+              (512, 768, 7168, 1), (4096, 768, 512, 1), (7168, 384, 2304, 1)]
+
+
+def _status_ok():
+    from eval_test_b200 import _lib
+    torch.cuda.synchronize()
+    st = _lib.device_status(torch.cuda.current_device())
+    assert st == 0, _lib.strerror(st)
+
+
+def _gemm(data, alpha=1.0):
+    from eval_test_b200 import nvfp4_gemm
+    out = nvfp4_gemm.custom_kernel(data, alpha=alpha)
+    _status_ok()
+    assert out is data[-1]
+    return out_np(out)
+
+
+def _dual(data, alpha=1.0):
+    from eval_test_b200 import nvfp4_dual_gemm
+    out = nvfp4_dual_gemm.custom_kernel(data, alpha=alpha)
+    _status_ok()
+    return out_np(out)
+
+
+def test_one_tile_one_k_iteration(oracle):
+    """Smallest case the kernel takes: pins nibble order, swizzles, descriptors and the scale layout."""
+    from eval_test_b200 import inputs
+    data = to_device(inputs.gemm_reference_style(128, 128, 256, 1, seed=1, device="cpu"))
+    got, want = _gemm(data), oracle.c_gemm(*gemm_oracle_args(data))
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("m,n,k,l", GEMM_TESTS)
+def test_gemm_reference_style_bit_exact(oracle, m, n, k, l):
+    """Dyadic inputs: fp32 accumulation is exact in any order, so the result must equal the oracle's bits."""
+    from eval_test_b200 import inputs
+    data = to_device(inputs.gemm_reference_style(m, n, k, l, seed=1111, device="cpu"))
+    got, want = _gemm(data), oracle.c_gemm(*gemm_oracle_args(data))
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("m,n,k,l,alpha", [(128, 256, 512, 1, 1.0), (200, 384, 768, 2, 0.5), (1000, 1280, 1024, 1, 0.5)])
+def test_gemm_quantized_within_tolerance(oracle, m, n, k, l, alpha):
+    """N(0,1) data through the quantiser (the first case is the CPU-runnable configuration), ragged M,
+    batches, alpha: rtol = atol = 1e-3 element-wise and max|d| <= 1e-2 max|ref|."""
+    from eval_test_b200 import check, inputs
+    data = to_device(inputs.gemm_quantized(m, n, k, l, seed=0, device="cpu"))
+    got = torch.from_numpy(_gemm(data, alpha))
+    want = torch.from_numpy(oracle.c_gemm(*gemm_oracle_args(data), alpha))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
+@pytest.mark.parametrize("m,n,k,l", DUAL_TESTS)
+def test_dual_gemm_reference_style(oracle, m, n, k, l):
+    """U[0,1) e4m3 scales (subnormals and zeros included): inexact in fp32, so the harness's tolerance."""
+    from eval_test_b200 import check, inputs
+    data = to_device(inputs.dual_gemm_reference_style(m, n, k, l, seed=1111, device="cpu"))
+    got = torch.from_numpy(_dual(data))
+    want = torch.from_numpy(oracle.c_dual_gemm(*dual_oracle_args(data)))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+
+
+def test_dual_gemm_quantized(oracle):
+    from eval_test_b200 import check, inputs
+    data = to_device(inputs.dual_gemm_quantized(384, 512, 1024, 2, seed=0, device="cpu"))
+    got = torch.from_numpy(_dual(data))
+    want = torch.from_numpy(oracle.c_dual_gemm(*dual_oracle_args(data)))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
+def test_large_gemm_rows_against_oracle(oracle):
+    """8192^3 with alpha = 0.5 (the large benchmark configuration): a 128-row band of the output is checked
+    against the oracle, the whole output through linearity in alpha."""
+    from eval_test_b200 import check, inputs, nvfp4_gemm
+    m = n = k = 8192
+    data = inputs.gemm_quantized(m, n, k, 1, seed=0, device="cuda")
+    a, b, _, _, sfa_p, sfb_p, c = data
+    c_half = nvfp4_gemm.custom_kernel(data, alpha=0.5).clone()
+    c_one = nvfp4_gemm.custom_kernel(data, alpha=1.0).clone()
+    _status_ok()
+    ok = (c_half.float().abs() > 1e-3) & (c_one.float().abs() < 3e4)
+    assert ok.float().mean() > 0.9
+    assert torch.equal((2 * c_half.float())[ok], c_one.float()[ok])
+    band = slice(128 * 17, 128 * 18)
+    from _util import operand_np, scales_np
+    sfa = scales_np(sfa_p).reshape(m // 128, -1)[17].reshape(-1)
+    want = torch.from_numpy(oracle.c_gemm(operand_np(a)[:, band], operand_np(b), sfa, scales_np(sfb_p), 0.5))
+    got = torch.from_numpy(out_np(c_half)[:, band])
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
+def test_gemm_bad_arguments():
+    from eval_test_b200 import _lib
+    lib = _lib.load()
+    p = torch.zeros(1 << 16, dtype=torch.uint8, device="cuda").data_ptr()
+    assert lib.nvfp4_gemm(p, p, p, p, p, 128, 128, 128, 1, 1.0, None) == -3    # K % 256
+    assert lib.nvfp4_gemm(p, p, p, p, p, 128, 64, 256, 1, 1.0, None) == -4     # N % 128
+    assert lib.nvfp4_gemm(p, p, p, p, None, 128, 128, 256, 1, 1.0, None) == -1
+    assert lib.nvfp4_dual_gemm(p, p, p, p, p, p, p, 0, 128, 256, 1, 1.0, None) == -2
