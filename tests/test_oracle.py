@@ -103,3 +103,39 @@ def test_config0_gemm_oracle_self_consistency(oracle):
     exact = (A @ B.T).numpy()
     rel = np.linalg.norm(c - exact) / np.linalg.norm(exact)
     assert 0.05 < rel < 0.25     # fp4 quantisation noise of two operands (about 0.13), far from 0 or 1
+
+
+# ------------------------------------------------------------------ pins against cuBLASLt outputs recorded on a B200
+def _gold():
+    from pathlib import Path
+    return np.load(Path(__file__).parent / "golden" / "scaled_mm_golden.npz")
+
+
+@pytest.mark.parametrize("tag", ["gemm0", "gemm1", "grp0", "grp1"])
+def test_oracle_matches_recorded_scaled_mm_dyadic(oracle, tag):
+    """Reference-style (dyadic) inputs: the oracle must reproduce torch._scaled_mm bit for bit - this pins the
+    nibble order, the e2m1 / e4m3 tables, the transposition and the scale layout."""
+    g = _gold()
+    for fn in (oracle.c_gemm, oracle.np_gemm):
+        got = fn(g[f"{tag}_a"], g[f"{tag}_b"], g[f"{tag}_sfa"], g[f"{tag}_sfb"])
+        assert np.array_equal(got.view(np.uint16), g[f"{tag}_c"].view(np.uint16))
+
+
+def test_oracle_matches_recorded_scaled_mm_gemv(oracle):
+    g = _gold()
+    for fn in (oracle.c_gemv, oracle.np_gemv):
+        got = fn(g["gemv_a"], g["gemv_x"], g["gemv_sfa"], g["gemv_sfx"])
+        assert np.array_equal(got.view(np.uint16), g["gemv_c"].view(np.uint16))
+
+
+def test_oracle_matches_recorded_scaled_mm_inexact(oracle):
+    """N(0,1)-quantised GEMM and the dual GEMM (U[0,1) scales): accumulation order inside the library is not
+    specified, so the harness's own tolerance (rtol = atol = 1e-3) applies."""
+    g = _gold()
+    got = oracle.c_gemm(g["gemmq_a"], g["gemmq_b"], g["gemmq_sfa"], g["gemmq_sfb"]).astype(np.float32)
+    want = g["gemmq_c"].astype(np.float32)
+    assert np.all(np.abs(got - want) <= 1e-3 + 1e-3 * np.abs(want))
+    got = oracle.c_dual_gemm(g["dual_a"], g["dual_b1"], g["dual_b2"], g["dual_sfa"], g["dual_sfb1"],
+                             g["dual_sfb2"]).astype(np.float32)
+    want = g["dual_c"].astype(np.float32)
+    assert np.all(np.abs(got - want) <= 1e-3 + 1e-3 * np.abs(want))
