@@ -25,7 +25,10 @@
 #include <stdint.h>
 #include <stdlib.h>
 
+#include <string.h>
+
 #include <mutex>
+#include <vector>
 
 #include "nvfp4_internal.h"
 #include "ptx_sm100.cuh"
@@ -37,6 +40,17 @@ constexpr int BK = 256;        // K elements per stage = 128 bytes per row = one
 constexpr int GEMM_THREADS = 192;
 constexpr uint32_t TMEM_COLS = 512;
 
+// One problem of a grouped GEMM as the kernel sees it (an array of these lives in device memory).
+struct alignas(64) GroupEntry {
+    CUtensorMap ta, tb;   // operand maps of this group (A: box 128 rows, B: box BN rows)
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    __half* c;            // [M][N]
+    int M, N, K;
+    int tile_start;       // index of this group's first tile in the launch-wide tile order
+    int tiles_m, tiles_n;
+};
+
 struct GemmParams {
     const uint8_t* sfa;   // swizzled scales of A  [L][ceil(M/128)][K/64][512]
     const uint8_t* sfb;   // swizzled scales of B (B1 for the dual GEMM)
@@ -46,6 +60,20 @@ struct GemmParams {
     float alpha;
     int* status;
     unsigned long long budget_ns;
+    const GroupEntry* table;  // grouped GEMM only: G entries, empty groups left out
+    int G;
+    int total_tiles;
+};
+
+// Everything a role needs to know about one output tile.
+struct TileInfo {
+    const CUtensorMap *ta, *tb, *tb2;
+    const uint8_t *sfa_t;     // scale block row of this tile's A rows (k = 0)
+    const uint8_t *sfb_t;     // scale block row of this tile's first 128 B rows (k = 0)
+    const uint8_t *sfb2_t;
+    __half* c;                // output of this problem / batch
+    size_t sf_row_block;      // bytes of one 128-row scale block = K/64 * 512
+    int M, N, kiters, l, m0, n0, nb_valid;
 };
 
 // Tile order: bands of 16 row-tiles; inside a band the row-tile index runs fastest, so the CTAs that
@@ -67,8 +95,115 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
 
 __device__ __forceinline__ float silu_mul(float x, float y) { return x / (1.0f + __expf(-x)) * y; }
 
+// Tile t of a plain / dual GEMM (all batches share the maps; the batch is the third TMA coordinate) or of a
+// grouped GEMM (binary search of the group whose tile range holds t; row-tile index fastest inside a group,
+// so the tiles that share a B column-tile run together and B streams from HBM once).
+template <int BN, bool DUAL, bool GROUPED>
+__device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUtensorMap* ta, const CUtensorMap* tb,
+                                           const CUtensorMap* tb2) {
+    constexpr int NB_BLOCKS = (DUAL ? 2 * BN : BN) / 128;
+    TileInfo ti;
+    if (GROUPED) {
+        int lo = 0, hi = p.G - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(&p.table[mid].tile_start) <= t) lo = mid; else hi = mid - 1;
+        }
+        const GroupEntry* e = p.table + lo;
+        const int r = t - __ldg(&e->tile_start);
+        const int tiles_m = __ldg(&e->tiles_m);
+        const int nt = r / tiles_m, mt = r - nt * tiles_m;
+        ti.ta = &e->ta; ti.tb = &e->tb; ti.tb2 = &e->tb;
+        ti.M = __ldg(&e->M); ti.N = __ldg(&e->N);
+        const int K = __ldg(&e->K);
+        ti.kiters = K / BK;
+        ti.sf_row_block = (size_t)(K / 64) * 512;
+        ti.l = 0; ti.m0 = mt * BM; ti.n0 = nt * BN;
+        ti.sfa_t = e->sfa + (size_t)mt * ti.sf_row_block;
+        ti.sfb_t = e->sfb + (size_t)(ti.n0 / 128) * ti.sf_row_block;
+        ti.sfb2_t = nullptr;
+        ti.c = e->c;
+        ti.nb_valid = min(NB_BLOCKS, ti.N / 128 - ti.n0 / 128);
+    } else {
+        const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        const int RB = p.N / 128;
+        ti.ta = ta; ti.tb = tb; ti.tb2 = tb2;
+        ti.M = p.M; ti.N = p.N; ti.kiters = p.K / BK;
+        ti.sf_row_block = (size_t)(p.K / 64) * 512;
+        ti.l = tc.l; ti.m0 = tc.mt * BM; ti.n0 = tc.nt * BN;
+        ti.sfa_t = p.sfa + ((size_t)tc.l * tiles_m + tc.mt) * ti.sf_row_block;
+        const size_t blk = (size_t)tc.l * RB + ti.n0 / 128;
+        ti.sfb_t = p.sfb + blk * ti.sf_row_block;
+        ti.sfb2_t = DUAL ? p.sfb2 + blk * ti.sf_row_block : nullptr;
+        ti.c = p.c + (size_t)tc.l * p.M * p.N;
+        ti.nb_valid = DUAL ? NB_BLOCKS : min(NB_BLOCKS, RB - ti.n0 / 128);
+    }
+    return ti;
+}
+
+// fp32 accumulator chunk(s) -> 32 fp16 outputs of one row, written as two whole 32-byte sectors
+// (16-byte stores left half-written sectors behind and cost 35 us at 8192^3).
+template <bool DUAL>
+__device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32], const uint32_t (&w)[32], float alpha,
+                                            bool pred) {
+    uint32_t o[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        __half2 h;
+        if (DUAL) {
+            const float x0 = alpha * __uint_as_float(v[2 * i]), x1 = alpha * __uint_as_float(v[2 * i + 1]);
+            const float y0 = alpha * __uint_as_float(w[2 * i]), y1 = alpha * __uint_as_float(w[2 * i + 1]);
+            h = __floats2half2_rn(silu_mul(x0, y0), silu_mul(x1, y1));
+        } else {
+            h = __floats2half2_rn(alpha * __uint_as_float(v[2 * i]), alpha * __uint_as_float(v[2 * i + 1]));
+        }
+        o[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    if (pred) {
+        const uint32_t lo[8] = {o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]};
+        const uint32_t hi[8] = {o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]};
+        st_global_256(dst, lo);
+        st_global_256(dst + 16, hi);
+    }
+}
+
+// Epilogue of one tile for one warp (its 32 accumulator rows).  C0 is the first 32-column chunk, relative to
+// the accumulator base, that this buffer shares with the other one (OVC chunks; OVC = 0: nothing shared).
+// The shared chunks are pulled into registers first and released at once, so the next tile's MMAs wait only
+// for those loads, not for the conversion and stores.
+template <int BN, bool DUAL, int C0, int OVC>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, bool row_ok, int n0, int N, float alpha,
+                                              uint32_t ovl_free, int lane) {
+    constexpr int NCH = BN / 32;
+    uint32_t ov[OVC > 0 ? OVC : 1][32];
+    if (OVC > 0) {
+#pragma unroll
+        for (int j = 0; j < OVC; j++) tc_ld_32x32(t_lane + (C0 + j) * 32, ov[j]);
+        tc_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ovl_free);
+    }
+#pragma unroll
+    for (int cc = 0; cc < NCH; cc++) {
+        constexpr int YOFF = BN / 32;  // dual GEMM: column chunk of the second product
+        uint32_t v[32], w[32];
+        const bool v_pre = OVC > 0 && cc >= C0 && cc < C0 + OVC;
+        const bool w_pre = DUAL && OVC > 0 && cc + YOFF >= C0 && cc + YOFF < C0 + OVC;
+        if (!v_pre) tc_ld_32x32(t_lane + cc * 32, v);
+        if (DUAL && !w_pre) tc_ld_32x32(t_lane + (cc + YOFF) * 32, w);
+        if (!v_pre || (DUAL && !w_pre)) tc_wait_ld();
+        const bool pred = row_ok && n0 + cc * 32 < N;
+        // (index clamps only keep the never-taken branch in range for the compiler)
+        store_chunk<DUAL>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+                          w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
+                          pred);
+    }
+}
+
 // BN: output columns per tile (GEMM: 128 or 256; DUAL: 128, the MMA is 256 wide over [B1;B2]).
-template <int BN, bool DUAL, int STAGES>
+template <int BN, bool DUAL, bool GROUPED, int STAGES>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
@@ -80,30 +215,44 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     constexpr uint32_t SFB_BYTES = NB_BLOCKS * 4 * 512;
     constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES + SFA_BYTES + SFB_BYTES;
     constexpr uint32_t SF_COLS = 16 + 4 * (MMA_N / 32);  // TMEM columns of one stage's scales
+    // Tensor memory: two accumulators and two alternating scale regions.  Two 256-column accumulators do
+    // not fit beside the scales, so the second one starts early and overlaps the tail of the first by
+    // OVERLAP columns; the epilogue drains the shared columns first and releases them on their own barrier.
+    constexpr uint32_t SF_BASE = TMEM_COLS - 2 * SF_COLS;
+    constexpr uint32_t ACC1_OFF = (2 * MMA_N <= SF_BASE) ? MMA_N : SF_BASE - MMA_N;
+    constexpr uint32_t OVERLAP = MMA_N - ACC1_OFF;
+    constexpr int OV_CHUNKS = OVERLAP / 32;             // 32-column chunks the two buffers share
     static_assert(MMA_N == 128 || MMA_N == 256, "MMA N");
-    static_assert(MMA_N + 2 * SF_COLS <= TMEM_COLS, "tensor memory");
+    static_assert(OVERLAP % 32 == 0 && ACC1_OFF % 32 == 0, "accumulator overlap");
 
     extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t bars[2 * STAGES + 2];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
     __shared__ uint32_t tmem_base_slot;
 
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
-    const uint32_t acc_full = smem_u32(&bars[2 * STAGES]), acc_empty = acc_full + 8;
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]);   // [2] accumulator complete
+    const uint32_t acc_empty0 = acc_full0 + 16;               // [2] accumulator drained
+    const uint32_t ovl_free = acc_full0 + 32;                 // shared columns drained (once per tile)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(acc_full, 1);
-        mbar_init(acc_empty, 4);  // one arrival per epilogue warp
+        for (int b = 0; b < 2; b++) {
+            mbar_init(acc_full0 + 8 * b, 1);
+            mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+        }
+        mbar_init(ovl_free, 4);
         fence_mbar_init();
-        prefetch_tmap(&tmap_a);
-        prefetch_tmap(&tmap_b);
-        if (DUAL) prefetch_tmap(&tmap_b2);
+        if (!GROUPED) {
+            prefetch_tmap(&tmap_a);
+            prefetch_tmap(&tmap_b);
+            if (DUAL) prefetch_tmap(&tmap_b2);
+        }
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tmem_base_slot), TMEM_COLS);
@@ -114,13 +263,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
-    const int tiles_m = (p.M + BM - 1) / BM;
-    const int tiles_n = (p.N + BN - 1) / BN;
-    const int total_tiles = tiles_m * tiles_n * p.L;
-    const int kiters = p.K / BK;
-    const int RA = tiles_m;                  // 128-row scale blocks of A per batch
-    const int RB = (p.N + 127) / 128;        // 128-row scale blocks of B per batch
-    const size_t sf_row_block = (size_t)(p.K / 64) * 512;   // bytes of one 128-row scale block
+    const int total_tiles = p.total_tiles;
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (one lane)
@@ -128,14 +271,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t it = 0;
             bool alive = true;
             for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
-                const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-                const int m0 = tc.mt * BM, n0 = tc.nt * BN;
-                const uint8_t* sfa_t = p.sfa + ((size_t)tc.l * RA + tc.mt) * sf_row_block;
-                // scale blocks of B rows [n0, n0 + BN): index of the first 128-row block
-                const size_t sfb_blk0 = (size_t)tc.l * RB + n0 / 128;
-                int nb_valid = NB_BLOCKS;  // 128-row blocks of the B tile that exist (N tail)
-                if (!DUAL) nb_valid = min(NB_BLOCKS, RB - n0 / 128);
-                for (int kit = 0; kit < kiters; kit++, it++) {
+                const TileInfo ti = locate<BN, DUAL, GROUPED>(t, p, &tmap_a, &tmap_b, &tmap_b2);
+                for (int kit = 0; kit < ti.kiters; kit++, it++) {
                     const int slot = it % STAGES;
                     if (!mbar_wait(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns)) {
                         report_status(p.status, DEV_TIMEOUT_PRODUCER);
@@ -148,23 +285,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sSFA = sB + B_BYTES;
                     const uint32_t sSFB = sSFA + SFA_BYTES;
                     const int k0 = kit * BK;
-                    const uint32_t tx = A_BYTES + B_BYTES + SFA_BYTES + (uint32_t)nb_valid * 2048u;
+                    const uint32_t tx = A_BYTES + B_BYTES + SFA_BYTES + (uint32_t)ti.nb_valid * 2048u;
                     mbar_arrive_expect_tx(full, tx);
-                    tma_load_3d(sA, &tmap_a, k0, m0, tc.l, full);
-                    if (DUAL) {
-                        tma_load_3d(sB, &tmap_b, k0, n0, tc.l, full);
-                        tma_load_3d(sB + BN * 128, &tmap_b2, k0, n0, tc.l, full);
-                    } else {
-                        tma_load_3d(sB, &tmap_b, k0, n0, tc.l, full);
-                    }
+                    tma_load_3d(sA, ti.ta, k0, ti.m0, ti.l, full);
+                    tma_load_3d(sB, ti.tb, k0, ti.n0, ti.l, full);
+                    if (DUAL) tma_load_3d(sB + BN * 128, ti.tb2, k0, ti.n0, ti.l, full);
                     const size_t koff = (size_t)(k0 / 64) * 512;
-                    bulk_g2s(sSFA, sfa_t + koff, 2048u, full);
+                    bulk_g2s(sSFA, ti.sfa_t + koff, 2048u, full);
                     if (DUAL) {
-                        bulk_g2s(sSFB, p.sfb + sfb_blk0 * sf_row_block + koff, 2048u, full);
-                        bulk_g2s(sSFB + 2048u, p.sfb2 + sfb_blk0 * sf_row_block + koff, 2048u, full);
+                        bulk_g2s(sSFB, ti.sfb_t + koff, 2048u, full);
+                        bulk_g2s(sSFB + 2048u, ti.sfb2_t + koff, 2048u, full);
                     } else {
-                        for (int j = 0; j < nb_valid; j++)
-                            bulk_g2s(sSFB + j * 2048u, p.sfb + (sfb_blk0 + j) * sf_row_block + koff, 2048u, full);
+                        for (int j = 0; j < ti.nb_valid; j++)
+                            bulk_g2s(sSFB + j * 2048u, ti.sfb_t + j * ti.sf_row_block + koff, 2048u, full);
                     }
                 }
             }
@@ -176,12 +309,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t it = 0, tile_it = 0;
             bool alive = true;
             for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x, tile_it++) {
-                // the epilogue must have drained the accumulator of the previous tile
-                if (!mbar_wait(acc_empty, (tile_it & 1) ^ 1, p.budget_ns)) {
+                // this buffer's previous tile (two tiles back) must be drained, and the previous tile's
+                // epilogue must have released the columns the two buffers share
+                const uint32_t buf = tile_it & 1;
+                bool ok = mbar_wait(acc_empty0 + 8 * buf, ((tile_it >> 1) & 1) ^ 1, p.budget_ns);
+                if (ok && OVERLAP > 0 && tile_it > 0) ok = mbar_wait(ovl_free, (tile_it - 1) & 1, p.budget_ns);
+                if (!ok) {
                     report_status(p.status, DEV_TIMEOUT_MMA_ACC);
                     break;
                 }
                 tc_fence_after_sync();
+                const uint32_t t_acc = tmem_base + buf * ACC1_OFF;
+                const int kiters = locate<BN, DUAL, GROUPED>(t, p, &tmap_a, &tmap_b, &tmap_b2).kiters;
                 for (int kit = 0; kit < kiters; kit++, it++) {
                     const int slot = it % STAGES;
                     if (!mbar_wait(full0 + 8 * slot, (it / STAGES) & 1, p.budget_ns)) {
@@ -195,7 +334,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sSFA = sB + B_BYTES;
                     const uint32_t sSFB = sSFA + SFA_BYTES;
                     // scales of this stage: two alternating TMEM regions after the accumulator columns
-                    const uint32_t t_sfa = tmem_base + MMA_N + (it & 1) * SF_COLS;
+                    const uint32_t t_sfa = tmem_base + SF_BASE + (it & 1) * SF_COLS;
                     const uint32_t t_sfb = t_sfa + 16;
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++) {
@@ -206,60 +345,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
 #pragma unroll
                     for (int ks = 0; ks < 4; ks++) {
-                        tc_mma_nvfp4(tmem_base, make_desc_k_sw128(sA + 32 * ks), make_desc_k_sw128(sB + 32 * ks), idesc,
+                        tc_mma_nvfp4(t_acc, make_desc_k_sw128(sA + 32 * ks), make_desc_k_sw128(sB + 32 * ks), idesc,
                                      t_sfa + 4 * ks, t_sfb + ks * (MMA_N / 32), (kit | ks) != 0 ? 1u : 0u);
                     }
                     tc_commit(empty0 + 8 * slot);  // frees the stage once these MMAs have read it
                 }
-                if (alive) tc_commit(acc_full);     // accumulator complete
+                if (alive) tc_commit(acc_full0 + 8 * buf);  // accumulator complete
             }
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps 2..5
         const int q = warp & 3;                      // TMEM lane quadrant this warp may access
-        const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
         uint32_t tile_it = 0;
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_it++) {
-            const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-            const int row = tc.mt * BM + q * 32 + lane;
-            const int n0 = tc.nt * BN;
-            if (!mbar_wait(acc_full, tile_it & 1, p.budget_ns)) {
+            const TileInfo ti = locate<BN, DUAL, GROUPED>(t, p, &tmap_a, &tmap_b, &tmap_b2);
+            const int row = ti.m0 + q * 32 + lane;
+            const int n0 = ti.n0;
+            const uint32_t buf = tile_it & 1;
+            if (!mbar_wait(acc_full0 + 8 * buf, (tile_it >> 1) & 1, p.budget_ns)) {
                 if (lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
                 break;
             }
             tc_fence_after_sync();
-            __half* crow = p.c + ((size_t)tc.l * p.M + (size_t)(row < p.M ? row : 0)) * p.N + n0;
-#pragma unroll 1
-            for (int cc = 0; cc < BN / 32; cc++) {
-                uint32_t v[32];
-                __align__(16) __half2 h[16];
-                tc_ld_32x32(t_lane + cc * 32, v);
-                if (DUAL) {
-                    uint32_t w[32];
-                    tc_ld_32x32(t_lane + BN + cc * 32, w);
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const float x0 = p.alpha * __uint_as_float(v[2 * i]), x1 = p.alpha * __uint_as_float(v[2 * i + 1]);
-                        const float y0 = p.alpha * __uint_as_float(w[2 * i]), y1 = p.alpha * __uint_as_float(w[2 * i + 1]);
-                        h[i] = __floats2half2_rn(silu_mul(x0, y0), silu_mul(x1, y1));
-                    }
-                } else {
-                    tc_wait_ld();
-#pragma unroll
-                    for (int i = 0; i < 16; i++)
-                        h[i] = __floats2half2_rn(p.alpha * __uint_as_float(v[2 * i]), p.alpha * __uint_as_float(v[2 * i + 1]));
-                }
-                if (row < p.M && n0 + cc * 32 < p.N) {
-                    uint4* dst = reinterpret_cast<uint4*>(crow + cc * 32);
-                    const uint4* src = reinterpret_cast<const uint4*>(h);
-#pragma unroll
-                    for (int i = 0; i < 4; i++) dst[i] = src[i];
-                }
-            }
+            const uint32_t t_lane = tmem_base + buf * ACC1_OFF + ((uint32_t)(q * 32) << 16);
+            __half* crow = ti.c + (size_t)(row < ti.M ? row : 0) * ti.N + n0;
+            // buffer 0 shares its last OVERLAP columns, buffer 1 its first
+            if (buf == 0)
+                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha,
+                                                                      ovl_free, lane);
+            else
+                epilogue_tile<BN, DUAL, 0, OV_CHUNKS>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free, lane);
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty);
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
         }
     }
 
@@ -274,22 +392,43 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------ host side
 // Tensor map over a packed-e2m1 operand [L][rows][K/2]: dimensions (K elements, rows, L), box
 // (256 elements = 128 bytes, box_rows, 1), 128-byte swizzle, out-of-range rows read as zero.
+// Encoding costs about a microsecond of host time, which matters for calls whose kernel runs for ten:
+// the last few maps are kept per thread, keyed by everything that goes into them.
 int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L, int box_rows) {
+    struct Key { const void* base; int rows, K, L, box; };
+    struct Entry { Key k; CUtensorMap m; bool valid; };
+    constexpr int WAYS = 8;
+    thread_local Entry cache[WAYS] = {};
+    thread_local int victim = 0;
+    for (int i = 0; i < WAYS; i++) {
+        const Entry& e = cache[i];
+        if (e.valid && e.k.base == base && e.k.rows == rows && e.k.K == K && e.k.L == L && e.k.box == box_rows) {
+            *map = e.m;
+            return NVFP4_OK;
+        }
+    }
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)rows, (uint64_t)L};
     const uint64_t strides[2] = {(uint64_t)(K / 2), (uint64_t)rows * (uint64_t)(K / 2)};
     const uint32_t box[3] = {256u, (uint32_t)box_rows, 1u};
-    return encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims, strides, box,
-                        CU_TENSOR_MAP_SWIZZLE_128B);
+    int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    Entry& v = cache[victim];
+    victim = (victim + 1) % WAYS;
+    v.k = Key{base, rows, K, L, box_rows};
+    v.m = *map;
+    v.valid = true;
+    return NVFP4_OK;
 }
 
-template <int BN, bool DUAL, int STAGES>
+template <int BN, bool DUAL, bool GROUPED, int STAGES>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                        cudaStream_t stream) {
     constexpr int MMA_N = DUAL ? 2 * BN : BN;
     constexpr size_t STAGE = 128 * 128 + MMA_N * 128 + 2048 + (MMA_N / 128) * 2048;
     constexpr size_t SMEM = STAGES * STAGE + 1024;  // + slack for the 1024-byte alignment
     static_assert(SMEM <= 227 * 1024 - 256, "shared memory");
-    auto kern = gemm_kernel<BN, DUAL, STAGES>;
+    auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -300,8 +439,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
         if (e != cudaSuccess) return (int)e;
         configured[dev] = true;
     }
-    const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.L;
-    const int grid = tiles < sm_count(dev) ? tiles : sm_count(dev);
+    if (p.total_tiles <= 0) return NVFP4_OK;
+    const int grid = p.total_tiles < sm_count(dev) ? p.total_tiles : sm_count(dev);
     kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, p);
     e = cudaGetLastError();
     return e == cudaSuccess ? NVFP4_OK : (int)e;
@@ -312,6 +451,7 @@ static int check_common(const void* const* ptrs, int nptr, int M, int N, int K, 
         if (!ptrs[i]) return NVFP4_ERR_NULL;
         if ((uintptr_t)ptrs[i] & 15) return NVFP4_ERR_ALIGN;
     }
+    if ((uintptr_t)ptrs[nptr - 1] & 31) return NVFP4_ERR_ALIGN;  // the output is written with 256-bit stores
     if (M <= 0 || N <= 0 || K <= 0 || L <= 0) return NVFP4_ERR_SHAPE;
     if (K % BK != 0) return NVFP4_ERR_K_MULTIPLE;
     if (N % 128 != 0) return NVFP4_ERR_N_MULTIPLE;
@@ -343,8 +483,10 @@ extern "C" int nvfp4_gemm(const void* a, const void* b, const void* sfa_sw, cons
     p.M = M; p.N = N; p.K = K; p.L = L; p.alpha = alpha;
     p.status = status_word(dev);
     p.budget_ns = wait_budget_ns();
-    if (wide) return launch_gemm<256, false, 4>(ta, tb, tb, p, (cudaStream_t)stream);
-    return launch_gemm<128, false, 6>(ta, tb, tb, p, (cudaStream_t)stream);
+    p.table = nullptr; p.G = 0;
+    p.total_tiles = ((M + BM - 1) / BM) * (N / (wide ? 256 : 128)) * L;
+    if (wide) return launch_gemm<256, false, false, 4>(ta, tb, tb, p, (cudaStream_t)stream);
+    return launch_gemm<128, false, false, 6>(ta, tb, tb, p, (cudaStream_t)stream);
 }
 
 extern "C" int nvfp4_dual_gemm(const void* a, const void* b1, const void* b2, const void* sfa_sw, const void* sfb1_sw,
@@ -367,5 +509,149 @@ extern "C" int nvfp4_dual_gemm(const void* a, const void* b1, const void* b2, co
     p.c = (__half*)c; p.M = M; p.N = N; p.K = K; p.L = L; p.alpha = alpha;
     p.status = status_word(dev);
     p.budget_ns = wait_budget_ns();
-    return launch_gemm<128, true, 4>(ta, tb1, tb2, p, (cudaStream_t)stream);
+    p.table = nullptr; p.G = 0;
+    p.total_tiles = ((M + BM - 1) / BM) * (N / 128) * L;
+    return launch_gemm<128, true, false, 4>(ta, tb1, tb2, p, (cudaStream_t)stream);
+}
+
+// ------------------------------------------------------------------------------------------ grouped GEMM
+namespace nvfp4 {
+namespace {
+
+// The problem table of a launch lives in device memory that the library owns: per device a small ring of
+// (pinned host staging buffer, device buffer, event) slots.  A slot is reused only after the launch that read it
+// has finished (its event), so concurrent streams and back-to-back calls never share a table.
+constexpr int TABLE_SLOTS = 8;
+struct TableSlot {
+    GroupEntry* host = nullptr;
+    GroupEntry* dev = nullptr;
+    int capacity = 0;
+    cudaEvent_t done = nullptr;
+    bool used = false;
+    // the call this slot's device table was built for: an identical call (same pointers and sizes, the usual
+    // case when a layer runs again) reuses the table without re-encoding or uploading anything
+    std::vector<nvfp4_group_t> key;
+    int live = 0, tiles = 0, bn = 0;
+};
+struct TableRing {
+    TableSlot slots[TABLE_SLOTS];
+    int next = 0;
+};
+std::mutex g_table_mu;
+TableRing g_rings[64];
+
+int acquire_slot(int dev, int G, TableSlot** out) {
+    TableRing& ring = g_rings[dev];
+    TableSlot& s = ring.slots[ring.next];
+    ring.next = (ring.next + 1) % TABLE_SLOTS;
+    s.key.clear();
+    cudaError_t e;
+    if (s.used) {
+        e = cudaEventSynchronize(s.done);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (!s.done) {
+        e = cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming);
+        if (e != cudaSuccess) return (int)e;
+    }
+    if (s.capacity < G) {
+        int cap = 64;
+        while (cap < G) cap *= 2;
+        if (s.host) cudaFreeHost(s.host);
+        if (s.dev) cudaFree(s.dev);
+        s.host = nullptr; s.dev = nullptr; s.capacity = 0;
+        e = cudaHostAlloc((void**)&s.host, sizeof(GroupEntry) * cap, cudaHostAllocDefault);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaMalloc((void**)&s.dev, sizeof(GroupEntry) * cap);
+        if (e != cudaSuccess) return (int)e;
+        s.capacity = cap;
+    }
+    *out = &s;
+    return NVFP4_OK;
+}
+
+}  // namespace
+}  // namespace nvfp4
+
+extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alpha, void* stream) {
+    if (!groups) return NVFP4_ERR_NULL;
+    if (G <= 0) return NVFP4_ERR_SHAPE;
+    if (G > 65536) return NVFP4_ERR_TOO_MANY_GROUPS;
+    bool wide = true;
+    int live = 0;
+    for (int g = 0; g < G; g++) {
+        const nvfp4_group_t& q = groups[g];
+        if (q.M < 0 || q.N <= 0 || q.K <= 0) return NVFP4_ERR_SHAPE;
+        if (q.K % BK != 0) return NVFP4_ERR_K_MULTIPLE;
+        if (q.N % 128 != 0) return NVFP4_ERR_N_MULTIPLE;
+        if (q.M == 0) continue;  // empty group: nothing to read or write
+        const void* ptrs[5] = {q.a, q.b, q.sfa_sw, q.sfb_sw, q.c};
+        for (const void* ptr : ptrs) {
+            if (!ptr) return NVFP4_ERR_NULL;
+            if ((uintptr_t)ptr & 15) return NVFP4_ERR_ALIGN;
+        }
+        if ((uintptr_t)q.c & 31) return NVFP4_ERR_ALIGN;
+        if (q.N % 256 != 0) wide = false;
+        live++;
+    }
+    if (live == 0) return NVFP4_OK;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
+    const int bn = wide ? 256 : 128;
+
+    std::lock_guard<std::mutex> lk(g_table_mu);
+    cudaStream_t st = (cudaStream_t)stream;
+    GemmParams p;
+    p.sfa = p.sfb = p.sfb2 = nullptr; p.c = nullptr;
+    p.M = p.N = p.K = 0; p.L = 1; p.alpha = alpha;
+    p.status = status_word(dev);
+    p.budget_ns = wait_budget_ns();
+    TableSlot* slot = nullptr;
+    for (TableSlot& cand : g_rings[dev].slots) {
+        if (cand.used && cand.key.size() == (size_t)G &&
+            memcmp(cand.key.data(), groups, sizeof(nvfp4_group_t) * G) == 0) {
+            slot = &cand;
+            break;
+        }
+    }
+    if (slot) {
+        p.table = slot->dev; p.G = slot->live; p.total_tiles = slot->tiles;
+        const CUtensorMap& dm = slot->host[0].ta;
+        int rc2 = slot->bn == 256 ? launch_gemm<256, false, true, 4>(dm, dm, dm, p, st)
+                                  : launch_gemm<128, false, true, 6>(dm, dm, dm, p, st);
+        e = cudaEventRecord(slot->done, st);
+        if (rc2) return rc2;
+        return e == cudaSuccess ? NVFP4_OK : (int)e;
+    }
+    int rc = acquire_slot(dev, live, &slot);
+    if (rc) return rc;
+    int tiles = 0, n = 0;
+    for (int g = 0; g < G; g++) {
+        const nvfp4_group_t& q = groups[g];
+        if (q.M == 0) continue;
+        GroupEntry& en = slot->host[n++];
+        rc = make_operand_tmap(&en.ta, q.a, q.M, q.K, 1, 128);
+        if (rc) return rc;
+        rc = make_operand_tmap(&en.tb, q.b, q.N, q.K, 1, bn);
+        if (rc) return rc;
+        en.sfa = (const uint8_t*)q.sfa_sw; en.sfb = (const uint8_t*)q.sfb_sw; en.c = (__half*)q.c;
+        en.M = q.M; en.N = q.N; en.K = q.K;
+        en.tiles_m = (q.M + BM - 1) / BM; en.tiles_n = q.N / bn;
+        en.tile_start = tiles;
+        tiles += en.tiles_m * en.tiles_n;
+    }
+    e = cudaMemcpyAsync(slot->dev, slot->host, sizeof(GroupEntry) * live, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return (int)e;
+    p.table = slot->dev; p.G = live; p.total_tiles = tiles;
+    slot->key.assign(groups, groups + G);
+    slot->live = live; slot->tiles = tiles; slot->bn = bn;
+    const CUtensorMap& dummy = slot->host[0].ta;
+    rc = wide ? launch_gemm<256, false, true, 4>(dummy, dummy, dummy, p, st)
+              : launch_gemm<128, false, true, 6>(dummy, dummy, dummy, p, st);
+    slot->used = true;
+    e = cudaEventRecord(slot->done, st);
+    if (rc) return rc;
+    return e == cudaSuccess ? NVFP4_OK : (int)e;
 }

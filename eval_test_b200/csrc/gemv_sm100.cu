@@ -19,7 +19,8 @@
 //     is the e2m1 nibble itself, its 3 low bits index an 8-entry table held in two registers, and
 //     its top bit (the sign) makes the permute return 0, so "positives" and (after flipping the
 //     sign bits) "negatives" come out as two unsigned byte vectors;
-//   * 4-way int8 dot products (exact) against the vector, which sits in shared memory as int8;
+//   * 4-way int8 dot products (exact) against the vector, which sits in shared memory as int8 twice
+//     (+x for the positives, -x for the negatives, so one accumulator takes both);
 //   * one fp32 FMA per 16-element block with sfa*sfx; lanes split K, rows are reduced by shuffles.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -56,13 +57,14 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 constexpr uint32_t LUT_LO = 0x03020100u;  // 2*|e2m1| for codes 0..3
 constexpr uint32_t LUT_HI = 0x0C080604u;  // 2*|e2m1| for codes 4..7
 
-// Exact dot product of 8 e2m1 elements (one 32-bit word of A) with 8 int8 values (2*x).
-__device__ __forceinline__ void dot8(uint32_t w, uint32_t x0, uint32_t x1, int& dpos, int& dneg) {
+// Exact dot product of 8 e2m1 elements (one 32-bit word of A) with 8 int8 values (x0,x1 = 2*x; n0,n1 = -2*x).
+__device__ __forceinline__ int dot8(uint32_t w, uint32_t x0, uint32_t x1, uint32_t n0, uint32_t n1, int d) {
     const uint32_t wn = w ^ 0x88888888u;
-    dpos = __dp4a((int)prmt(LUT_LO, LUT_HI, w), (int)x0, dpos);
-    dpos = __dp4a((int)prmt(LUT_LO, LUT_HI, w >> 16), (int)x1, dpos);
-    dneg = __dp4a((int)prmt(LUT_LO, LUT_HI, wn), (int)x0, dneg);
-    dneg = __dp4a((int)prmt(LUT_LO, LUT_HI, wn >> 16), (int)x1, dneg);
+    d = __dp4a((int)prmt(LUT_LO, LUT_HI, w), (int)x0, d);
+    d = __dp4a((int)prmt(LUT_LO, LUT_HI, w >> 16), (int)x1, d);
+    d = __dp4a((int)prmt(LUT_LO, LUT_HI, wn), (int)n0, d);
+    d = __dp4a((int)prmt(LUT_LO, LUT_HI, wn >> 16), (int)n1, d);
+    return d;
 }
 
 __device__ __forceinline__ float2 e4m3x2_to_float2(uint16_t v) {
@@ -95,9 +97,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int K = p.K, M = p.M;
     const int kbs = K / 16;
     uint8_t* xs = smem;                                   // K int8: 2*x
-    float* sxs = reinterpret_cast<float*>(smem + K);      // K/16 floats: 0.25 * sfx
+    uint8_t* xn = smem + K;                               // K int8: -2*x
+    float* sxs = reinterpret_cast<float*>(smem + 2 * K);  // K/16 floats: 0.25 * sfx
     // ring: 1024-byte aligned (the swizzled scale slices need it)
-    uint8_t* ring = smem + (((smem_u32(smem) + K + kbs * 4 + 1023u) & ~1023u) - smem_u32(smem));
+    uint8_t* ring = smem + (((smem_u32(smem) + 2 * K + kbs * 4 + 1023u) & ~1023u) - smem_u32(smem));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
@@ -189,10 +192,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 for (int w4 = threadIdx.x; w4 < K / 8; w4 += CW * 32) {
                     const uint32_t w = reinterpret_cast<const uint32_t*>(xg)[w4];
                     const uint32_t wn = w ^ 0x88888888u;
-                    uint2 o;
-                    o.x = __vsub4(prmt(LUT_LO, LUT_HI, w), prmt(LUT_LO, LUT_HI, wn));
-                    o.y = __vsub4(prmt(LUT_LO, LUT_HI, w >> 16), prmt(LUT_LO, LUT_HI, wn >> 16));
-                    reinterpret_cast<uint2*>(xs)[w4] = o;
+                    const uint32_t p0 = prmt(LUT_LO, LUT_HI, w), p1 = prmt(LUT_LO, LUT_HI, w >> 16);
+                    const uint32_t q0 = prmt(LUT_LO, LUT_HI, wn), q1 = prmt(LUT_LO, LUT_HI, wn >> 16);
+                    reinterpret_cast<uint2*>(xs)[w4] = make_uint2(__vsub4(p0, q0), __vsub4(p1, q1));
+                    reinterpret_cast<uint2*>(xn)[w4] = make_uint2(__vsub4(q0, p0), __vsub4(q1, p1));
                 }
                 for (int kb = threadIdx.x; kb < kbs; kb += CW * 32) {
                     const uint8_t b = sg[(size_t)(kb >> 2) * 512 + (kb & 3)];
@@ -211,6 +214,17 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             float acc[RPW];
 #pragma unroll
             for (int rr = 0; rr < RPW; rr++) acc[rr] = 0.f;
+            // per-row offsets inside a stage, for segment `lane` of a 1024-element sub-chunk:
+            // A: row ur, 16 bytes per segment; scales: slice q = lane/2 (+16 per sub-chunk), 16-byte chunk i
+            // (XOR q%8 in the swizzled tiled layout; 16*sub keeps q%8), word g, byte pair lane%2
+            int aoff[RPW], soff[RPW];
+#pragma unroll
+            for (int rr = 0; rr < RPW; rr++) {
+                const int ur = warp * RPW + rr, q = lane >> 1;
+                aoff[rr] = St::A_OFF + ur * (KC / 2) + lane * 16;
+                soff[rr] = (TILED ? q * 128 + ((((ur & 7) ^ (q & 7)) << 4) | ((ur >> 3) << 2))
+                                  : q * SF_SLOT + (((ur & 7) << 4) | ((ur >> 3) << 2))) + (lane & 1) * 2;
+            }
 
             for (int c = 0; c < nchunks; c++, it++) {
                 const int slot = it % STAGES;
@@ -223,33 +237,28 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const int k0 = c * KC;
                 const int kc = min(KC, K - k0);
                 const uint8_t* Ss = ring + (size_t)slot * STAGE;
-                const uint8_t* As = Ss + St::A_OFF;
 #pragma unroll
                 for (int sub = 0; sub < KC / 1024; sub++) {
-                    const int seg = sub * 32 + lane;  // 32-element segment of this chunk
-                    if (MODE == 0 && seg * 32 < kc) {
-                        const int kg = k0 + seg * 32;
+                    const int kseg = sub * 1024 + lane * 32;  // this lane's 32-element segment of the chunk
+                    if (MODE == 0 && kseg < kc) {
+                        const int kg = k0 + kseg;
                         const uint4 xa = *reinterpret_cast<const uint4*>(xs + kg);
                         const uint4 xb = *reinterpret_cast<const uint4*>(xs + kg + 16);
+                        const uint4 na = *reinterpret_cast<const uint4*>(xn + kg);
+                        const uint4 nb = *reinterpret_cast<const uint4*>(xn + kg + 16);
                         const float2 sx = *reinterpret_cast<const float2*>(sxs + (kg >> 4));
 #pragma unroll
                         for (int rr = 0; rr < RPW; rr++) {
-                            const int ur = warp * RPW + rr;  // unit row = 8*g + i
-                            const uint4 av = *reinterpret_cast<const uint4*>(As + ur * (KC / 2) + seg * 16);
-                            // scale slice of 64-element group q = seg/2: 16-byte chunk i, word g, bytes kb%4;
-                            // the tiled path stores 128-byte rows with chunk index XOR (q % 8)
-                            const int q = seg >> 1;
-                            const int sfoff = TILED ? q * 128 + ((((ur & 7) ^ (q & 7)) << 4) | ((ur >> 3) << 2))
-                                                    : q * SF_SLOT + (((ur & 7) << 4) | ((ur >> 3) << 2));
-                            const uint16_t sfw = *reinterpret_cast<const uint16_t*>(Ss + sfoff + (seg & 1) * 2);
+                            const uint4 av = *reinterpret_cast<const uint4*>(Ss + aoff[rr] + sub * 512);
+                            const uint16_t sfw = *reinterpret_cast<const uint16_t*>(
+                                Ss + soff[rr] + sub * 16 * (TILED ? 128 : SF_SLOT));
                             const float2 sa = e4m3x2_to_float2(sfw);
-                            int p0 = 0, n0 = 0, p1 = 0, n1 = 0;
-                            dot8(av.x, xa.x, xa.y, p0, n0);
-                            dot8(av.y, xa.z, xa.w, p0, n0);
-                            dot8(av.z, xb.x, xb.y, p1, n1);
-                            dot8(av.w, xb.z, xb.w, p1, n1);
-                            acc[rr] = fmaf((float)(p0 - n0), sa.x * sx.x, acc[rr]);
-                            acc[rr] = fmaf((float)(p1 - n1), sa.y * sx.y, acc[rr]);
+                            int d0 = dot8(av.x, xa.x, xa.y, na.x, na.y, 0);
+                            d0 = dot8(av.y, xa.z, xa.w, na.z, na.w, d0);
+                            int d1 = dot8(av.z, xb.x, xb.y, nb.x, nb.y, 0);
+                            d1 = dot8(av.w, xb.z, xb.w, nb.z, nb.w, d1);
+                            acc[rr] = fmaf((float)d0, sa.x * sx.x, acc[rr]);
+                            acc[rr] = fmaf((float)d1, sa.y * sx.y, acc[rr]);
                         }
                     }
                 }
@@ -279,7 +288,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
     const bool tiled = (p.M % 128 == 0);
     const int stage = tiled ? GemvStage<KC, true>::BYTES : GemvStage<KC, false>::BYTES;
-    const size_t smem = (size_t)p.K + (size_t)(p.K / 16) * 4 + 1024 + (size_t)STAGES * stage;
+    const size_t smem = 2 * (size_t)p.K + (size_t)(p.K / 16) * 4 + 1024 + (size_t)STAGES * stage;
     if (smem > 227 * 1024 - 256) return NVFP4_ERR_UNSUPPORTED;
     const int RB = (p.M + 127) / 128;
     const int Kb4 = (p.K / 16 + 3) / 4;
@@ -337,7 +346,7 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
     if (K % 64 != 0) return NVFP4_ERR_K_MULTIPLE;
     if (((uintptr_t)a | (uintptr_t)x | (uintptr_t)sfa_sw | (uintptr_t)sfx_sw) & 15) return NVFP4_ERR_ALIGN;
     if ((uintptr_t)c & 1) return NVFP4_ERR_ALIGN;
-    if (K > 65536) return NVFP4_ERR_UNSUPPORTED;  // the vector (int8) must fit in shared memory beside the ring
+    if (K > 65536) return NVFP4_ERR_UNSUPPORTED;  // the vector (int8, twice) must fit in shared memory beside the ring
     GemvParams p;
     p.a = (const uint8_t*)a; p.x = (const uint8_t*)x; p.sfa = (const uint8_t*)sfa_sw; p.sfx = (const uint8_t*)sfx_sw;
     p.c = (__half*)c; p.M = M; p.K = K; p.L = L; p.x_rows = x_rows; p.alpha = alpha;
@@ -348,7 +357,8 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
     p.budget_ns = wait_budget_ns();
     cudaStream_t s = (cudaStream_t)stream;
     static const int variant = [] { const char* e = getenv("NVFP4_GEMV_VARIANT"); return e ? atoi(e) : 0; }();
-    if (K > 32768) return launch_gemv<8, 2048, 3>(p, s);
+    if (K > 32768) return launch_gemv<8, 1024, 3>(p, s);
+    if (K > 16384) return launch_gemv<8, 2048, 4>(p, s);
     switch (variant) {  // tuning knob; 0 is the shipped configuration
         case 1: return launch_gemv<16, 2048, 5>(p, s);
         case 2: return launch_gemv<8, 4096, 2>(p, s);
@@ -359,6 +369,10 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
         case 7: return launch_gemv<8, 4096, 2, 1, 1>(p, s);
         case 8: return launch_gemv<8, 1024, 4, 2, 1>(p, s);
         case 9: return launch_gemv<16, 4096, 2>(p, s);
-        default: return launch_gemv<8, 2048, 5>(p, s);
+        case 10: return launch_gemv<8, 1024, 5, 2>(p, s);
+        case 11: return launch_gemv<8, 1024, 3, 2>(p, s);
+        case 12: return launch_gemv<8, 2048, 2, 2>(p, s);
+        case 13: return launch_gemv<16, 1024, 4, 1>(p, s);
+        default: return launch_gemv<8, 1024, 4, 2>(p, s);
     }
 }
