@@ -45,62 +45,289 @@ def measured_peaks() -> tuple[float, str]:
 
 
 # ----------------------------------------------------------------------------------------------- workloads
+def _util():
+    sys.path.insert(0, str(ROOT / "tests"))
+    import _util
+    return _util
+
+
 class GemvWorkload:
-    """c1: A 16384 x 16384 e2m1 with block-16 e4m3 scales times a quantised vector, batch 4."""
+    """Batched GEMV: A 16384 x 16384 e2m1 with block-16 e4m3 scales times a quantised vector, batch 4.
+    N > 1: every rank owns 16384 more rows of A (weak scaling, nothing exchanged)."""
     name = "gemv_m16384_k16384_l4"
     metric = "nvfp4_gemv_hbm_gbs"
-    unit = "GB/s"
+    unit, per = "GB/s", 1e9
     dtype = "e2m1 x ue4m3 scales, int32 block dot, fp32 accumulate, fp16 out"
-    bound = "hbm"
-    kernel = "gemv_kernel"
+    bound, kernel, scaling = "hbm", "gemv_kernel", "weak"
 
     def __init__(self, m=16384, k=16384, l=4):
         self.m, self.k, self.l = m, k, l
 
-    def bytes_per_step(self, m=None) -> int:
-        """Algorithmic bytes: A + its scales + the vector and its scales + the fp16 output, per batch."""
-        m = self.m if m is None else m
-        per_batch = m * self.k // 2 + m * self.k // 16 + (self.k // 2 + self.k // 16) + 2 * m
-        return self.l * per_batch
+    def small(self):
+        return GemvWorkload(m=4096, k=self.k, l=self.l)
 
-    def make(self, seed, device):
+    def work(self, world=1, m=None) -> int:
+        """Algorithmic bytes per rank and step: A + its scales + the vector and its scales + the fp16 output."""
+        m = self.m if m is None else m
+        return self.l * (m * self.k // 2 + m * self.k // 16 + (self.k // 2 + self.k // 16) + 2 * m)
+
+    def job(self, world=1) -> int:
+        return self.work() * world
+
+    def make(self, rank, world, device):
         from eval_test_b200 import inputs
-        return inputs.gemv_quantized(self.m, self.k, self.l, seed=seed, device=device)
+        return inputs.gemv_quantized(self.m, self.k, self.l, seed=rank, device=device)
 
     def run(self, data):
         from eval_test_b200 import nvfp4_gemv
         return nvfp4_gemv.custom_kernel(data)
 
-    def io_tensors(self, data):
+    def io(self, data):
         a, b, _, _, sfa_p, sfb_p, c = data
-        return [a, b, sfa_p, sfb_p], c
+        return [a, b, sfa_p, sfb_p], [c]
 
-    def rebuild(self, data, moved):
+    def with_inputs(self, data, moved):
         a, b, sfa, sfb, sfa_p, sfb_p, c = data
         return (moved[0], moved[1], sfa, sfb, moved[2], moved[3], c)
 
-    def config(self, n_gpus):
-        return {"workload": self.name, "m_per_gpu": self.m, "k": self.k, "l": self.l,
-                "global_m": self.m * n_gpus, "sharding": "rows of A per rank, no collective",
-                "l2": "inputs (604 MB per step) larger than L2 (126 MB)",
-                "generator": "N(0,1) seed 0 -> block-16 quantiser (scale = amax/6 as e4m3, RNE e2m1)"}
+    def config(self, world):
+        return {"workload": self.name, "m_per_gpu": self.m, "k": self.k, "l": self.l, "global_m": self.m * world,
+                "sharding": "rows of A per rank, no collective",
+                "l2": f"inputs ({self.work() / 1e6:.0f} MB per step) larger than L2 (126 MB)",
+                "generator": "N(0,1) seed = rank -> block-16 quantiser (scale = amax/6 as e4m3, RNE e2m1)"}
 
-    # CPU side (oracle) -----------------------------------------------------------------------------
-    def cpu_sample(self, data, rows):
-        """Rows [0, rows) of every batch as oracle arrays (rows is a multiple of 128)."""
-        sys.path.insert(0, str(ROOT / "tests"))
-        from _util import operand_np, scales_np
+    def cpu_sample(self, data, rows=2048):
+        u = _util()
+        rows = min(rows, self.m)
         a, b, _, _, sfa_p, sfb_p, _ = data
-        a_np = operand_np(a[:rows])
-        sfa = scales_np(sfa_p[:, :, : rows // 128])
-        return a_np, operand_np(b), sfa, scales_np(sfb_p)
+        args = (u.operand_np(a[:rows]), u.operand_np(b), u.scales_np(sfa_p[:, :, : rows // 128]), u.scales_np(sfb_p))
+        return args, self.work(m=rows), f"rows 0..{rows - 1} of each of the {self.l} batches, K = {self.k}"
 
-    def cpu_run(self, sample):
+    def cpu_data(self, rows=2048):
+        from eval_test_b200 import inputs
+        return inputs.gemv_quantized(min(rows, self.m), self.k, self.l, seed=0, device="cpu")
+
+    def cpu_run(self, args):
         from oracle import nvfp4_oracle as O
-        return O.c_gemv(*sample)
+        return O.c_gemv(*args)
 
 
-WORKLOADS = {"gemv": GemvWorkload}
+class GemmWorkload:
+    """Large GEMM: M = N = K = 8192, alpha = 0.5.  N > 1: B, its scales and C are split along N (strong scaling,
+    no K split, so nothing is reduced or exchanged)."""
+    name = "gemm_m8192_n8192_k8192"
+    metric = "nvfp4_gemm_tflops"
+    unit, per = "TFLOPS", 1e12
+    dtype = "e2m1 x ue4m3 scales on tcgen05 (kind::mxf4nvf4), fp32 accumulate, fp16 out"
+    bound, kernel, scaling = "tensor", "gemm_kernel", "strong"
+    alpha = 0.5
+
+    def __init__(self, m=8192, n=8192, k=8192):
+        self.m, self.n, self.k = m, n, k
+
+    def small(self):
+        return GemmWorkload(m=4096, n=8192, k=4096)
+
+    def work(self, world=1, m=None, n=None) -> int:
+        return 2 * (self.m if m is None else m) * (self.n // world if n is None else n) * self.k
+
+    def job(self, world=1) -> int:
+        return self.work(1)
+
+    def make(self, rank, world, device):
+        from eval_test_b200 import inputs
+        import torch
+        a, _, sfa, _, sfa_p, _, _ = inputs.gemm_quantized(self.m, 128, self.k, 1, seed=0, device=device)
+        g = torch.Generator(device=device).manual_seed(1000 + rank)
+        b, sfb, sfb_p = inputs.quantized_operand(1, self.n // world, self.k, g, device)
+        c = torch.empty((1, self.m, self.n // world), dtype=torch.float16, device=device).permute(1, 2, 0)
+        return (a, b, sfa, sfb, sfa_p, sfb_p, c)
+
+    def run(self, data):
+        from eval_test_b200 import nvfp4_gemm
+        return nvfp4_gemm.custom_kernel(data, alpha=self.alpha)
+
+    def io(self, data):
+        a, b, _, _, sfa_p, sfb_p, c = data
+        return [a, b, sfa_p, sfb_p], [c]
+
+    def with_inputs(self, data, moved):
+        a, b, sfa, sfb, sfa_p, sfb_p, c = data
+        return (moved[0], moved[1], sfa, sfb, moved[2], moved[3], c)
+
+    def config(self, world):
+        return {"workload": self.name, "m": self.m, "n": self.n, "k": self.k, "l": 1, "alpha": self.alpha,
+                "n_per_gpu": self.n // world, "sharding": "columns of C (rows of B) per rank, A replicated, no collective",
+                "l2": "operands + output (210 MB at 1 GPU) larger than L2 (126 MB)",
+                "generator": "N(0,1) seeded -> block-16 quantiser"}
+
+    def cpu_sample(self, data, rows=128, cols=1024):
+        u = _util()
+        a, b, _, _, sfa_p, sfb_p, _ = data
+        cols = min(cols, b.shape[0])
+        args = (u.operand_np(a[:rows]), u.operand_np(b[:cols]), u.scales_np(sfa_p[:, :, : rows // 128]),
+                u.scales_np(sfb_p[:, :, : cols // 128]), self.alpha)
+        return args, self.work(m=rows, n=cols), f"rows 0..{rows - 1} of A against rows 0..{cols - 1} of B, K = {self.k}"
+
+    def cpu_data(self, rows=128, cols=1024):
+        from eval_test_b200 import inputs
+        return inputs.gemm_quantized(rows, cols, self.k, 1, seed=0, device="cpu")
+
+    def cpu_run(self, args):
+        from oracle import nvfp4_oracle as O
+        return O.c_gemm(*args)
+
+
+class DualGemmWorkload(GemmWorkload):
+    """SwiGLU up-projection: C = silu(A.B1) * (A.B2), A 4096 x 4096, B1 and B2 14336 x 4096."""
+    name = "dual_gemm_m4096_n14336_k4096"
+    metric = "nvfp4_dual_gemm_tflops"
+    kernel = "gemm_kernel"
+    alpha = 1.0
+
+    def __init__(self, m=4096, n=14336, k=4096):
+        super().__init__(m, n, k)
+
+    def small(self):
+        return DualGemmWorkload(m=2048, n=7168, k=4096)
+
+    def work(self, world=1, m=None, n=None) -> int:
+        return 2 * super().work(world, m, n)
+
+    def make(self, rank, world, device):
+        from eval_test_b200 import inputs
+        import torch
+        a, _, sfa, _, sfa_p, _, _ = inputs.gemm_quantized(self.m, 128, self.k, 1, seed=0, device=device)
+        g = torch.Generator(device=device).manual_seed(1000 + rank)
+        n = self.n // world
+        b1, sfb1, sfb1_p = inputs.quantized_operand(1, n, self.k, g, device)
+        b2, sfb2, sfb2_p = inputs.quantized_operand(1, n, self.k, g, device)
+        c = torch.empty((1, self.m, n), dtype=torch.float16, device=device).permute(1, 2, 0)
+        return (a, b1, b2, sfa, sfb1, sfb2, sfa_p, sfb1_p, sfb2_p, c)
+
+    def run(self, data):
+        from eval_test_b200 import nvfp4_dual_gemm
+        return nvfp4_dual_gemm.custom_kernel(data)
+
+    def io(self, data):
+        a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, c = data
+        return [a, b1, b2, sfa_p, sfb1_p, sfb2_p], [c]
+
+    def with_inputs(self, data, moved):
+        return (moved[0], moved[1], moved[2], data[3], data[4], data[5], moved[3], moved[4], moved[5], data[9])
+
+    def config(self, world):
+        cfg = super().config(world)
+        cfg.pop("alpha")
+        cfg["l2"] = "operands + output (193 MB at 1 GPU) larger than L2 (126 MB)"
+        return cfg
+
+    def cpu_sample(self, data, rows=128, cols=512):
+        u = _util()
+        a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, _ = data
+        cols = min(cols, b1.shape[0])
+        nb = cols // 128
+        args = (u.operand_np(a[:rows]), u.operand_np(b1[:cols]), u.operand_np(b2[:cols]),
+                u.scales_np(sfa_p[:, :, : rows // 128]), u.scales_np(sfb1_p[:, :, :nb]), u.scales_np(sfb2_p[:, :, :nb]))
+        return args, self.work(m=rows, n=cols), f"rows 0..{rows - 1} of A against rows 0..{cols - 1} of B1, B2"
+
+    def cpu_data(self, rows=128, cols=512):
+        from eval_test_b200 import inputs
+        return inputs.dual_gemm_quantized(rows, cols, self.k, 1, seed=0, device="cpu")
+
+    def cpu_run(self, args):
+        from oracle import nvfp4_oracle as O
+        return O.c_dual_gemm(*args)
+
+class GroupedGemmWorkload:
+    """MoE expert layer: 64 groups, N = 4096, K = 7168, M_g ~ Poisson(128) clipped to [0, 1024] from
+    numpy.random.default_rng(0).  At this M the layer is HBM-bound (every weight byte is read once), so the
+    metric is algorithmic GB/s.  N > 1: groups are dealt round-robin to the ranks (strong scaling)."""
+    name = "grouped_gemm_g64_n4096_k7168_poisson128"
+    metric = "nvfp4_grouped_gemm_hbm_gbs"
+    unit, per = "GB/s", 1e9
+    dtype = "e2m1 x ue4m3 scales on tcgen05 (kind::mxf4nvf4), fp32 accumulate, fp16 out"
+    bound, kernel, scaling = "hbm", "gemm_kernel", "strong"
+
+    def __init__(self, g=64, n=4096, k=7168, mean=128.0):
+        from eval_test_b200 import inputs
+        self.g, self.n, self.k = g, n, k
+        self.ms = inputs.poisson_group_sizes(g, mean, 0, 1024, seed=0)
+
+    def small(self):
+        return GroupedGemmWorkload(g=16)
+
+    def _mine(self, rank, world):
+        return self.ms[rank::world]
+
+    def _bytes(self, ms, n=None):
+        n, k = (self.n if n is None else n), self.k
+        w = sum(n * k // 2 + n * k // 16 for m in ms if m > 0)
+        return w + sum(m * k // 2 + (m + 127) // 128 * 128 * k // 16 + 2 * m * n for m in ms)
+
+    def work(self, world=1) -> int:
+        """Algorithmic bytes of the busiest rank: weights and their scales of every non-empty group, activations,
+        their (128-row padded) scales and the fp16 outputs."""
+        return max(self._bytes(self._mine(r, world)) for r in range(world))
+
+    def job(self, world=1) -> int:
+        return self._bytes(self.ms)
+
+    def make(self, rank, world, device):
+        from eval_test_b200 import inputs
+        ms = self._mine(rank, world)
+        return inputs.grouped_gemm_quantized(ms, [self.n] * len(ms), [self.k] * len(ms), len(ms), seed=rank,
+                                             device=device)
+
+    def run(self, data):
+        from eval_test_b200 import nvfp4_grouped_gemm
+        return nvfp4_grouped_gemm.custom_kernel(data)
+
+    def io(self, data):
+        abc, _, sfs_p, _ = data
+        ins = [t for (a, b, _), (sa, sb) in zip(abc, sfs_p) for t in (a, b, sa, sb) if t.numel()]
+        return ins, [c for (_, _, c) in abc if c.numel()]
+
+    def with_inputs(self, data, moved):
+        abc, sfs, sfs_p, sizes = data
+        it = iter(moved)
+        new_abc, new_p = [], []
+        for (a, b, c), (sa, sb) in zip(abc, sfs_p):
+            a2, b2, sa2, sb2 = (next(it) if t.numel() else t for t in (a, b, sa, sb))
+            new_abc.append((a2, b2, c))
+            new_p.append((sa2, sb2))
+        return (new_abc, sfs, new_p, sizes)
+
+    def config(self, world):
+        return {"workload": self.name, "groups": self.g, "n": self.n, "k": self.k, "sum_m": sum(self.ms),
+                "min_m": min(self.ms), "max_m": max(self.ms), "empty_groups": sum(m == 0 for m in self.ms),
+                "flop_per_step": sum(2 * m * self.n * self.k for m in self.ms),
+                "sharding": "groups dealt round-robin to ranks, no collective",
+                "l2": f"weights ({self.work() / 1e6:.0f} MB per step) larger than L2 (126 MB)",
+                "generator": "M_g = clip(Poisson(128), 0, 1024), numpy default_rng(0); operands N(0,1) -> quantiser"}
+
+    def cpu_sample(self, data, groups=2, cols=256):
+        u = _util()
+        abc, _, sfs_p, _ = data
+        args = []
+        for (a, b, _), (sa, sb) in list(zip(abc, sfs_p))[:groups]:
+            args.append((u.operand_np(a)[0], u.operand_np(b[:cols])[0], u.scales_np(sa),
+                         u.scales_np(sb[:, :, : cols // 128])))
+        ms = [a[0].shape[0] for a in args]
+        return args, self._bytes(ms, n=cols), f"groups 0..{groups - 1}, rows 0..{cols - 1} of each B, K = {self.k}"
+
+    def cpu_data(self, groups=2, cols=256):
+        from eval_test_b200 import inputs
+        ms = self.ms[:groups]
+        return inputs.grouped_gemm_quantized(ms, [cols] * groups, [self.k] * groups, groups, seed=0, device="cpu")
+
+    def cpu_run(self, args):
+        from oracle import nvfp4_oracle as O
+        return O.c_grouped_gemm(args)
+
+
+WORKLOADS = {"gemv": GemvWorkload, "gemm": GemmWorkload, "dual_gemm": DualGemmWorkload,
+             "grouped_gemm": GroupedGemmWorkload}
 
 
 # ----------------------------------------------------------------------------------------------- clocks
@@ -154,64 +381,68 @@ class ClockSampler:
 
 
 # ----------------------------------------------------------------------------------------------- CPU arm
-def cpu_baseline(wl, data, budget_s=20.0):
-    """Oracle on the host cores over a bounded sample (whole 128-row blocks of every batch)."""
-    from oracle import nvfp4_oracle as O
-    O.build()
-    rows = min(wl.m, 2048)
-    sample = wl.cpu_sample(data, rows)
+def _time_cpu(wl, args, budget_s=20.0):
     t0 = time.perf_counter()
-    wl.cpu_run(sample)
-    dt = time.perf_counter() - t0
-    # grow the sample towards a few seconds of work, then keep the best of 3
-    while dt < 1.0 and rows < wl.m:
-        rows = min(wl.m, rows * 4)
-        sample = wl.cpu_sample(data, rows)
-        t0 = time.perf_counter()
-        wl.cpu_run(sample)
-        dt = time.perf_counter() - t0
-    best = dt
+    wl.cpu_run(args)
+    best = time.perf_counter() - t0
     for _ in range(2):
         if best * 3 > budget_s:
             break
         t0 = time.perf_counter()
-        wl.cpu_run(sample)
+        wl.cpu_run(args)
         best = min(best, time.perf_counter() - t0)
-    return {"value": wl.bytes_per_step(rows) / best / 1e9, "unit": wl.unit, "cores": O.num_threads(),
-            "kind": "port", "sample": f"rows 0..{rows - 1} of each of the {wl.l} batches, K = {wl.k}; best of 3",
-            "seconds": best}
+    return best
+
+
+def cpu_baseline(wl, data):
+    """The CPU oracle on the host cores over a bounded sample of the same inputs (best of 3)."""
+    from oracle import nvfp4_oracle as O
+    O.build()
+    args, units, what = wl.cpu_sample(data)
+    best = _time_cpu(wl, args)
+    return {"value": units / best / wl.per, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
+            "sample": what + "; best of 3", "seconds": best}
 
 
 def run_reference(args, wl):
-    """Reference arm: the CPU oracle, all host threads, bounded sample per step (rank 0 only)."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """Reference arm: the reference has no CPU implementation of this path (its oracle is a cuBLASLt call), so
+    this times the CPU restatement of it with all host threads; each step is a bounded sample (rank 0 only)."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    import torch
     from oracle import nvfp4_oracle as O
     O.build()
-    rows = 2048
-    small = type(wl)(m=rows, k=wl.k, l=wl.l)
-    data = small.make(seed=0, device="cpu")
-    sample = small.cpu_sample(data, rows)
+    data = wl.cpu_data()
+    sample, units, what = wl.cpu_sample(data)
     for _ in range(max(1, min(args.warmup, 2))):
-        small.cpu_run(sample)
+        wl.cpu_run(sample)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        small.cpu_run(sample)
+        wl.cpu_run(sample)
     dt = (time.perf_counter() - t0) / args.steps
-    val = small.bytes_per_step() / dt / 1e9
+    val = units / dt / wl.per
     line = {"impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
             "config": wl.config(args.gpus),
             "cpu_baseline": {"value": val, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
-                             "sample": f"each step = rows 0..{rows - 1} of each of the {wl.l} batches, K = {wl.k}"},
+                             "sample": "each step = " + what},
             "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
+def tensor_peak_tflops() -> tuple[float, str]:
+    """Dense FP4 ceiling used for tensor-bound workloads: 4 x the measured bf16 GEMM rate of this pool (the
+    FP4 tensor path issues 4 x the bf16 flops per clock: 9 vs 2.25 PFLOP/s nominal)."""
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return 4.0 * float(json.loads(p.read_text())["bf16_tflops"]), "4 x measured bf16 burst"
+        except Exception:
+            pass
+    return 4.0 * 1590.0, "4 x fallback bf16"
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -225,7 +456,7 @@ def main():
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]()
     if args.small:
-        wl = GemvWorkload(m=4096, k=16384, l=4)
+        wl = wl.small()
 
     if args.impl == "reference":
         run_reference(args, wl)
@@ -252,7 +483,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    data = wl.make(seed=rank, device=dev)
+    data = wl.make(rank, world, dev)
     stream = torch.cuda.current_stream()
 
     for _ in range(args.warmup):
@@ -276,29 +507,30 @@ def main():
     status = _lib.device_status(local_rank)
     assert status == 0, f"device status {status}: {_lib.strerror(status)}"
 
-    # ---- end to end: pinned host inputs -> device, kernel, output -> host, every step ----
+    # ---- end to end: pinned host inputs -> device, kernel, outputs -> host, every step ----
     def flat(t):
         """All elements of a dense (possibly permuted) tensor as one 1-D view over its memory."""
         return torch.as_strided(t if t.dtype == torch.float16 else t.view(torch.uint8), (t.numel(),), (1,),
                                 t.storage_offset())
 
-    ins, out = wl.io_tensors(data)
+    ins, outs = wl.io(data)
     host_in = [torch.empty(t.numel(), dtype=torch.uint8).pin_memory() for t in ins]
     for h, t in zip(host_in, ins):
         h.copy_(flat(t))
-    host_out = torch.empty(out.numel(), dtype=out.dtype).pin_memory()
+    host_out = [torch.empty(o.numel(), dtype=o.dtype).pin_memory() for o in outs]
     dev_in = [torch.empty_like(t) for t in ins]
     for d, t in zip(dev_in, ins):
         assert d.stride() == t.stride()
-    e2e_data = wl.rebuild(data, dev_in)
+    e2e_data = wl.with_inputs(data, dev_in)
     h2d = sum(t.numel() * t.element_size() for t in ins)
-    d2h = out.numel() * out.element_size()
+    d2h = sum(o.numel() * o.element_size() for o in outs)
 
     def e2e_step():
         for d, h in zip(dev_in, host_in):
             flat(d).copy_(h, non_blocking=True)
-        res = wl.run(e2e_data)
-        host_out.copy_(flat(res), non_blocking=True)
+        wl.run(e2e_data)
+        for h, o in zip(host_out, outs):
+            h.copy_(flat(o), non_blocking=True)
 
     e2e_steps = 1 if args.small else args.e2e_steps
     for _ in range(0 if args.small else 2):
@@ -319,19 +551,26 @@ def main():
     total_ms, kern_ms, e2e_ms = (float(v) for v in t.tolist())
 
     if rank == 0:
-        peak, peak_kind = measured_peaks()
-        step_bytes = wl.bytes_per_step()
+        if wl.bound == "hbm":
+            peak, peak_kind = measured_peaks()
+            peak_unit = "GB/s"
+        else:
+            peak, peak_kind = tensor_peak_tflops()
+            peak_unit = "TFLOP/s"
+        units = wl.work(world)               # per rank (the busiest one)
+        job = wl.job(world)                  # whole job, all ranks
         ms_per_step = total_ms / args.steps
-        achieved = step_bytes / (kern_ms * 1e-3) / 1e9
+        achieved = units / (kern_ms * 1e-3) / wl.per
         line = {
-            "metric": wl.metric, "value": world * step_bytes / (ms_per_step * 1e-3) / 1e9, "unit": wl.unit,
+            "metric": wl.metric, "value": job / (ms_per_step * 1e-3) / wl.per, "unit": wl.unit,
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype,
+            "higher_is_better": True, "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic", "config": wl.config(world),
             "roofline": {"bound": wl.bound, "kernel": wl.kernel, "achieved": achieved, "peak": peak,
-                         "peak_kind": f"of {peak_kind}", "unit": "GB/s", "frac": achieved / peak,
-                         "bytes_per_launch": step_bytes, "us_per_launch": kern_ms * 1e3, "traffic": None},
-            "e2e": {"value": world * step_bytes / (e2e_ms * 1e-3) / 1e9, "unit": wl.unit,
+                         "peak_kind": peak_kind if wl.bound == "tensor" else f"of {peak_kind}", "unit": peak_unit,
+                         "frac": achieved / peak, "units_per_launch": units, "us_per_launch": kern_ms * 1e3,
+                         "traffic": None},
+            "e2e": {"value": job / (e2e_ms * 1e-3) / wl.per, "unit": wl.unit,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks.summary(),
