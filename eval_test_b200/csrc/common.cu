@@ -49,6 +49,12 @@ int* status_word(int dev) {
     return g_status_dev[dev];
 }
 
+int* status_word_if_allocated(int dev) {
+    if (dev < 0 || dev >= MAX_DEV) return nullptr;
+    std::lock_guard<std::mutex> lk(g_mu);
+    return g_status_dev[dev];
+}
+
 unsigned long long wait_budget_ns() {
     static unsigned long long v = [] {
         const char* e = getenv("NVFP4_WAIT_BUDGET_MS");

@@ -655,3 +655,97 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     if (rc) return rc;
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
+
+// ------------------------------------------------------------------------------------------ grouped GEMM, no allocation
+// Some callers cannot let this library allocate: a serving process whose own allocator has already claimed
+// all of HBM (a cudaMalloc from a library would fail, or would have to be carved out of the budget up front),
+// or a real-time loop that must not meet the implicit device-wide synchronisation of cudaMalloc / cudaFree.
+// nvfp4_grouped_gemm() keeps its problem tables in memory it allocates on first use; the variant below keeps
+// ONE table in a fixed array that is part of the library image, so every GPU that loads the library holds
+// these bytes until the process exits, whether or not the entry point is ever called.
+namespace nvfp4 {
+namespace {
+
+constexpr int STATIC_MAX_GROUPS = 256;  // non-empty groups per call (256 * 320 B = 80 KB of device memory)
+static __device__ __align__(256) unsigned char g_static_table[STATIC_MAX_GROUPS * sizeof(GroupEntry)];
+
+// In host code the array's name is only a handle for the runtime, not a device address: the address the
+// kernel needs comes from cudaGetSymbolAddress, asked once per device with that device current.
+GroupEntry* g_static_table_addr[64] = {};
+std::mutex g_static_mu;
+GroupEntry g_static_host[STATIC_MAX_GROUPS];  // host image of the table (plain pageable memory)
+
+}  // namespace
+
+// Status word of a device if an earlier call has already created it, else nullptr (defined in common.cu).
+int* status_word_if_allocated(int dev);
+
+}  // namespace nvfp4
+
+extern "C" int nvfp4_grouped_gemm_noalloc(const nvfp4_group_t* groups, int G, float alpha, void* stream) {
+    if (!groups) return NVFP4_ERR_NULL;
+    if (G <= 0) return NVFP4_ERR_SHAPE;
+    bool wide = true;
+    int live = 0;
+    for (int g = 0; g < G; g++) {
+        const nvfp4_group_t& q = groups[g];
+        if (q.M < 0 || q.N <= 0 || q.K <= 0) return NVFP4_ERR_SHAPE;
+        if (q.K % BK != 0) return NVFP4_ERR_K_MULTIPLE;
+        if (q.N % 128 != 0) return NVFP4_ERR_N_MULTIPLE;
+        if (q.M == 0) continue;
+        const void* ptrs[5] = {q.a, q.b, q.sfa_sw, q.sfb_sw, q.c};
+        for (const void* ptr : ptrs) {
+            if (!ptr) return NVFP4_ERR_NULL;
+            if ((uintptr_t)ptr & 15) return NVFP4_ERR_ALIGN;
+        }
+        if ((uintptr_t)q.c & 31) return NVFP4_ERR_ALIGN;
+        if (q.N % 256 != 0) wide = false;
+        live++;
+    }
+    if (live > STATIC_MAX_GROUPS) return NVFP4_ERR_TOO_MANY_GROUPS;  // the fixed table holds 256 non-empty groups
+    if (live == 0) return NVFP4_OK;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
+    const int bn = wide ? 256 : 128;
+
+    std::lock_guard<std::mutex> lk(g_static_mu);
+    if (!g_static_table_addr[dev]) {
+        // first call on this device: resolve the array's device address (do this before any stream capture)
+        void* ptr = nullptr;
+        e = cudaGetSymbolAddress(&ptr, g_static_table);
+        if (e != cudaSuccess) return (int)e;
+        g_static_table_addr[dev] = (GroupEntry*)ptr;
+    }
+    GroupEntry* table = g_static_table_addr[dev];
+    int tiles = 0, n = 0;
+    for (int g = 0; g < G; g++) {
+        const nvfp4_group_t& q = groups[g];
+        if (q.M == 0) continue;
+        GroupEntry& en = g_static_host[n++];
+        int rc = make_operand_tmap(&en.ta, q.a, q.M, q.K, 1, 128);
+        if (rc) return rc;
+        rc = make_operand_tmap(&en.tb, q.b, q.N, q.K, 1, bn);
+        if (rc) return rc;
+        en.sfa = (const uint8_t*)q.sfa_sw; en.sfb = (const uint8_t*)q.sfb_sw; en.c = (__half*)q.c;
+        en.M = q.M; en.N = q.N; en.K = q.K;
+        en.tiles_m = (q.M + BM - 1) / BM; en.tiles_n = q.N / bn;
+        en.tile_start = tiles;
+        tiles += en.tiles_m * en.tiles_n;
+    }
+    cudaStream_t st = (cudaStream_t)stream;
+    // From pageable memory this copy is staged by the runtime before it returns, so the host image may be
+    // rewritten by the next call at once.  Only entries [0, live) are ever read: nothing needs clearing.
+    e = cudaMemcpyAsync(table, g_static_host, sizeof(GroupEntry) * live, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return (int)e;
+    GemmParams p;
+    p.sfa = p.sfb = p.sfb2 = nullptr; p.c = nullptr;
+    p.M = p.N = p.K = 0; p.L = 1; p.alpha = alpha;
+    p.status = status_word_if_allocated(dev);
+    p.budget_ns = wait_budget_ns();
+    p.table = table; p.G = live; p.total_tiles = tiles;
+    const CUtensorMap& dm = g_static_host[0].ta;
+    return wide ? launch_gemm<256, false, true, 4>(dm, dm, dm, p, st)
+                : launch_gemm<128, false, true, 6>(dm, dm, dm, p, st);
+}

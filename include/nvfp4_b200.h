@@ -80,6 +80,21 @@ typedef struct nvfp4_group {
  * eval/nvfp4_grouped_gemm/reference.py:137-201). */
 int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alpha, void* stream);
 
+/* The same grouped GEMM for callers that must not let the library allocate memory (a process whose own
+ * allocator already owns all of HBM; a loop that cannot afford the device-wide synchronisation of
+ * cudaMalloc / cudaFree).  Same arguments and results as nvfp4_grouped_gemm.  No counterpart in the reference.
+ *  - The problem table lives in ONE fixed device array inside the library image (80 KB, held by every GPU that
+ *    loads the library until the process exits): at most 256 non-empty groups per call, more are refused with
+ *    NVFP4_ERR_TOO_MANY_GROUPS.
+ *  - It calls no cudaMalloc / cudaFree / cudaHostAlloc and creates no events.  The first call on a device
+ *    resolves the array's device address; make that call before any stream capture.
+ *  - Every call rewrites the same array (the previous call's entries stay behind, only the first `live`
+ *    entries are read): calls that overlap on the GPU - different streams - race; keep them on one stream or
+ *    order them yourself.
+ *  - A device-side wait that expires is recorded only if an earlier call of another entry point has already
+ *    created the device's status word; the kernel still returns instead of hanging. */
+int nvfp4_grouped_gemm_noalloc(const nvfp4_group_t* groups, int G, float alpha, void* stream);
+
 /* Last device-side status code of device `dev` (0 = none); clear != 0 resets it.
  * Call after synchronising the stream.  No counterpart in the reference, whose kernels spin
  * without bound (eval/nvfp4_grouped_gemm/submission.py:91-104). */
