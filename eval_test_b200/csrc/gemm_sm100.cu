@@ -63,7 +63,18 @@ struct GemmParams {
     const GroupEntry* table;  // grouped GEMM only: G entries, empty groups left out
     int G;
     int total_tiles;
+#ifdef NVFP4_PROFILE
+    unsigned long long* prof = nullptr;  // per CTA: cycles the MMA issuer spent waiting for accumulators / for data / in total
+#endif
 };
+
+#ifdef NVFP4_PROFILE
+#define PROF_T0() const long long prof_t0_ = clock64()
+#define PROF_ADD(var) var += clock64() - prof_t0_
+#else
+#define PROF_T0()
+#define PROF_ADD(var)
+#endif
 
 // Everything a role needs to know about one output tile.
 struct TileInfo {
@@ -308,12 +319,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             constexpr uint32_t idesc = make_idesc_nvfp4(BM, MMA_N);
             uint32_t it = 0, tile_it = 0;
             bool alive = true;
+#ifdef NVFP4_PROFILE
+            long long prof_acc = 0, prof_full = 0;
+            const long long prof_begin = clock64();
+#endif
             for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x, tile_it++) {
                 // this buffer's previous tile (two tiles back) must be drained, and the previous tile's
                 // epilogue must have released the columns the two buffers share
                 const uint32_t buf = tile_it & 1;
-                bool ok = mbar_wait(acc_empty0 + 8 * buf, ((tile_it >> 1) & 1) ^ 1, p.budget_ns);
-                if (ok && OVERLAP > 0 && tile_it > 0) ok = mbar_wait(ovl_free, (tile_it - 1) & 1, p.budget_ns);
+                bool ok;
+                {
+                    PROF_T0();
+                    ok = mbar_wait(acc_empty0 + 8 * buf, ((tile_it >> 1) & 1) ^ 1, p.budget_ns);
+                    if (ok && OVERLAP > 0 && tile_it > 0) ok = mbar_wait(ovl_free, (tile_it - 1) & 1, p.budget_ns);
+                    PROF_ADD(prof_acc);
+                }
                 if (!ok) {
                     report_status(p.status, DEV_TIMEOUT_MMA_ACC);
                     break;
@@ -323,7 +343,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 const int kiters = locate<BN, DUAL, GROUPED>(t, p, &tmap_a, &tmap_b, &tmap_b2).kiters;
                 for (int kit = 0; kit < kiters; kit++, it++) {
                     const int slot = it % STAGES;
-                    if (!mbar_wait(full0 + 8 * slot, (it / STAGES) & 1, p.budget_ns)) {
+                    bool got;
+                    {
+                        PROF_T0();
+                        got = mbar_wait(full0 + 8 * slot, (it / STAGES) & 1, p.budget_ns);
+                        PROF_ADD(prof_full);
+                    }
+                    if (!got) {
                         report_status(p.status, DEV_TIMEOUT_CONSUMER);
                         alive = false;
                         break;
@@ -352,6 +378,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                 }
                 if (alive) tc_commit(acc_full0 + 8 * buf);  // accumulator complete
             }
+#ifdef NVFP4_PROFILE
+            if (p.prof) {
+                p.prof[3 * blockIdx.x + 0] = prof_acc;
+                p.prof[3 * blockIdx.x + 1] = prof_full;
+                p.prof[3 * blockIdx.x + 2] = clock64() - prof_begin;
+            }
+#endif
         }
     } else {
         // ------------------------------------------------------------------ epilogue warps 2..5
@@ -485,6 +518,9 @@ extern "C" int nvfp4_gemm(const void* a, const void* b, const void* sfa_sw, cons
     p.budget_ns = wait_budget_ns();
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N / (wide ? 256 : 128)) * L;
+#ifdef NVFP4_PROFILE
+    { const char* e_ = getenv("NVFP4_PROF_PTR"); p.prof = e_ ? (unsigned long long*)strtoull(e_, nullptr, 0) : nullptr; }
+#endif
     if (wide) return launch_gemm<256, false, false, 4>(ta, tb, tb, p, (cudaStream_t)stream);
     return launch_gemm<128, false, false, 6>(ta, tb, tb, p, (cudaStream_t)stream);
 }
