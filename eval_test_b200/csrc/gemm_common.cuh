@@ -1,0 +1,207 @@
+// Declarations shared by the tcgen05 GEMM kernels (one CTA per tile, and CTA pairs): launch parameters, the
+// grouped-GEMM problem table entry, tile location and the epilogue.
+#pragma once
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "nvfp4_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace nvfp4 {
+
+constexpr int BM = 128;        // rows of A per tile = TMEM lanes
+constexpr int BK = 256;        // K elements per stage = 128 bytes per row = one swizzle atom
+constexpr int GEMM_THREADS = 192;
+constexpr uint32_t TMEM_COLS = 512;
+
+// One problem of a grouped GEMM as the kernel sees it (an array of these lives in device memory).
+struct alignas(64) GroupEntry {
+    CUtensorMap ta, tb;   // operand maps of this group (A: box 128 rows, B: box BN rows)
+    const uint8_t* sfa;
+    const uint8_t* sfb;
+    __half* c;            // [M][N]
+    int M, N, K;
+    int tile_start;       // index of this group's first tile in the launch-wide tile order
+    int tiles_m, tiles_n;
+};
+
+struct GemmParams {
+    const uint8_t* sfa;   // swizzled scales of A  [L][ceil(M/128)][K/64][512]
+    const uint8_t* sfb;   // swizzled scales of B (B1 for the dual GEMM)
+    const uint8_t* sfb2;  // swizzled scales of B2 (dual GEMM only)
+    __half* c;            // [L][M][N]
+    int M, N, K, L;
+    float alpha;
+    int* status;
+    unsigned long long budget_ns;
+    const GroupEntry* table;  // grouped GEMM only: G entries, empty groups left out
+    int G;
+    int total_tiles;
+#ifdef NVFP4_PROFILE
+    unsigned long long* prof = nullptr;  // per CTA: cycles the MMA issuer spent waiting for accumulators / for data / in total
+#endif
+};
+
+#ifdef NVFP4_PROFILE
+#define PROF_T0() const long long prof_t0_ = clock64()
+#define PROF_ADD(var) var += clock64() - prof_t0_
+#else
+#define PROF_T0()
+#define PROF_ADD(var)
+#endif
+
+// Everything a role needs to know about one output tile.
+struct TileInfo {
+    const CUtensorMap *ta, *tb, *tb2;
+    const uint8_t *sfa_t;     // scale block row of this tile's A rows (k = 0)
+    const uint8_t *sfb_t;     // scale block row of this tile's first 128 B rows (k = 0)
+    const uint8_t *sfb2_t;
+    __half* c;                // output of this problem / batch
+    size_t sf_row_block;      // bytes of one 128-row scale block = K/64 * 512
+    int M, N, kiters, l, m0, n0, nb_valid;
+};
+
+// Tile order: bands of 16 row-tiles; inside a band the row-tile index runs fastest, so the CTAs that
+// run together share a few A row-tiles and B column-tiles in L2.
+struct TileCoord { int l, mt, nt; };
+__device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n) {
+    constexpr int BAND = 16;
+    const int per_l = tiles_m * tiles_n;
+    TileCoord tc;
+    tc.l = t / per_l;
+    int r = t - tc.l * per_l;
+    const int band = r / (BAND * tiles_n);
+    r -= band * BAND * tiles_n;
+    const int rows_in_band = min(BAND, tiles_m - band * BAND);
+    tc.nt = r / rows_in_band;
+    tc.mt = band * BAND + (r - tc.nt * rows_in_band);
+    return tc;
+}
+
+__device__ __forceinline__ float silu_mul(float x, float y) { return x / (1.0f + __expf(-x)) * y; }
+
+// Tile t of a plain / dual GEMM (all batches share the maps; the batch is the third TMA coordinate) or of a
+// grouped GEMM (binary search of the group whose tile range holds t; row-tile index fastest inside a group,
+// so the tiles that share a B column-tile run together and B streams from HBM once).
+template <int BN, bool DUAL, bool GROUPED>
+__device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUtensorMap* ta, const CUtensorMap* tb,
+                                           const CUtensorMap* tb2) {
+    constexpr int NB_BLOCKS = (DUAL ? 2 * BN : BN) / 128;
+    TileInfo ti;
+    if (GROUPED) {
+        int lo = 0, hi = p.G - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(&p.table[mid].tile_start) <= t) lo = mid; else hi = mid - 1;
+        }
+        const GroupEntry* e = p.table + lo;
+        const int r = t - __ldg(&e->tile_start);
+        const int tiles_m = __ldg(&e->tiles_m);
+        const int nt = r / tiles_m, mt = r - nt * tiles_m;
+        ti.ta = &e->ta; ti.tb = &e->tb; ti.tb2 = &e->tb;
+        ti.M = __ldg(&e->M); ti.N = __ldg(&e->N);
+        const int K = __ldg(&e->K);
+        ti.kiters = K / BK;
+        ti.sf_row_block = (size_t)(K / 64) * 512;
+        ti.l = 0; ti.m0 = mt * BM; ti.n0 = nt * BN;
+        ti.sfa_t = e->sfa + (size_t)mt * ti.sf_row_block;
+        ti.sfb_t = e->sfb + (size_t)(ti.n0 / 128) * ti.sf_row_block;
+        ti.sfb2_t = nullptr;
+        ti.c = e->c;
+        ti.nb_valid = min(NB_BLOCKS, ti.N / 128 - ti.n0 / 128);
+    } else {
+        const int tiles_m = (p.M + BM - 1) / BM, tiles_n = (p.N + BN - 1) / BN;
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        const int RB = p.N / 128;
+        ti.ta = ta; ti.tb = tb; ti.tb2 = tb2;
+        ti.M = p.M; ti.N = p.N; ti.kiters = p.K / BK;
+        ti.sf_row_block = (size_t)(p.K / 64) * 512;
+        ti.l = tc.l; ti.m0 = tc.mt * BM; ti.n0 = tc.nt * BN;
+        ti.sfa_t = p.sfa + ((size_t)tc.l * tiles_m + tc.mt) * ti.sf_row_block;
+        const size_t blk = (size_t)tc.l * RB + ti.n0 / 128;
+        ti.sfb_t = p.sfb + blk * ti.sf_row_block;
+        ti.sfb2_t = DUAL ? p.sfb2 + blk * ti.sf_row_block : nullptr;
+        ti.c = p.c + (size_t)tc.l * p.M * p.N;
+        ti.nb_valid = DUAL ? NB_BLOCKS : min(NB_BLOCKS, RB - ti.n0 / 128);
+    }
+    return ti;
+}
+
+// fp32 accumulator chunk(s) -> 32 fp16 outputs of one row, written as two whole 32-byte sectors
+// (16-byte stores left half-written sectors behind and cost 35 us at 8192^3).
+template <bool DUAL>
+__device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32], const uint32_t (&w)[32], float alpha,
+                                            bool pred) {
+    uint32_t o[16];
+#pragma unroll
+    for (int i = 0; i < 16; i++) {
+        __half2 h;
+        if (DUAL) {
+            const float x0 = alpha * __uint_as_float(v[2 * i]), x1 = alpha * __uint_as_float(v[2 * i + 1]);
+            const float y0 = alpha * __uint_as_float(w[2 * i]), y1 = alpha * __uint_as_float(w[2 * i + 1]);
+            h = __floats2half2_rn(silu_mul(x0, y0), silu_mul(x1, y1));
+        } else {
+            h = __floats2half2_rn(alpha * __uint_as_float(v[2 * i]), alpha * __uint_as_float(v[2 * i + 1]));
+        }
+        o[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    if (pred) {
+        const uint32_t lo[8] = {o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]};
+        const uint32_t hi[8] = {o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]};
+        // written once, never read by this kernel: evict-first keeps the operands in L2 instead
+        const uint64_t pol = policy_evict_first();
+        st_global_256_hint(dst, lo, pol);
+        st_global_256_hint(dst + 16, hi, pol);
+    }
+}
+
+// Epilogue of one tile for one warp (its 32 accumulator rows).  C0 is the first 32-column chunk, relative to
+// the accumulator base, that this buffer shares with the other one (OVC chunks; OVC = 0: nothing shared).
+// The shared chunks are pulled into registers first and released at once, so the next tile's MMAs wait only
+// for those loads, not for the conversion and stores.
+// CLUSTER: ovl_free is a shared::cluster address (the barrier may live in the peer CTA).
+template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false>
+__device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, bool row_ok, int n0, int N, float alpha,
+                                              uint32_t ovl_free, int lane) {
+    constexpr int NCH = BN / 32;
+    uint32_t ov[OVC > 0 ? OVC : 1][32];
+    if (OVC > 0) {
+#pragma unroll
+        for (int j = 0; j < OVC; j++) tc_ld_32x32(t_lane + (C0 + j) * 32, ov[j]);
+        tc_wait_ld();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+            if (CLUSTER) mbar_arrive_cluster(ovl_free);
+            else mbar_arrive(ovl_free);
+        }
+    }
+#pragma unroll
+    for (int cc = 0; cc < NCH; cc++) {
+        constexpr int YOFF = BN / 32;  // dual GEMM: column chunk of the second product
+        uint32_t v[32], w[32];
+        const bool v_pre = OVC > 0 && cc >= C0 && cc < C0 + OVC;
+        const bool w_pre = DUAL && OVC > 0 && cc + YOFF >= C0 && cc + YOFF < C0 + OVC;
+        if (!v_pre) tc_ld_32x32(t_lane + cc * 32, v);
+        if (DUAL && !w_pre) tc_ld_32x32(t_lane + (cc + YOFF) * 32, w);
+        if (!v_pre || (DUAL && !w_pre)) tc_wait_ld();
+        const bool pred = row_ok && n0 + cc * 32 < N;
+        // (index clamps only keep the never-taken branch in range for the compiler)
+        store_chunk<DUAL>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+                          w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
+                          pred);
+    }
+}
+
+// Tensor map over a packed-e2m1 operand [L][rows][K/2] (defined in gemm_sm100.cu).
+int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L, int box_rows);
+
+// CTA-pair kernels (gemm_pair_sm100.cu).  pair_tiles_wanted(): true when the shape suits them (M >= 256, enough
+// 256-row tiles to fill the machine).  launch_gemm_pair(): maps with 128-row boxes.
+bool pair_kernel_suits(int M, int N, int K, int L, bool dual, int dev);
+int launch_gemm_pair(bool dual, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
+                     cudaStream_t stream);
+
+}  // namespace nvfp4

@@ -19,8 +19,11 @@
 //     is the e2m1 nibble itself, its 3 low bits index an 8-entry table held in two registers, and
 //     its top bit (the sign) makes the permute return 0, so "positives" and (after flipping the
 //     sign bits) "negatives" come out as two unsigned byte vectors;
-//   * 4-way int8 dot products (exact) against the vector, which sits in shared memory as int8 twice
-//     (+x for the positives, -x for the negatives, so one accumulator takes both);
+//     the two tables are biased so that the permute's by-products cancel: positives look up v+1 (v = 2*|a|,
+//     0 stays 0) and negatives -v; a positive element makes the negative lookup return -1 (replicated MSB of
+//     a negative table byte), a negative element makes the positive lookup return 0, so the two byte vectors
+//     always add up to the signed value and both can be fed to dp4a against the same vector;
+//   * 4-way int8 dot products (exact) against the vector, which sits in shared memory as int8;
 //   * one fp32 FMA per 16-element block with sfa*sfx; lanes split K, rows are reduced by shuffles.
 #include <cuda_fp16.h>
 #include <cuda_fp8.h>
@@ -56,14 +59,18 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 
 constexpr uint32_t LUT_LO = 0x03020100u;  // 2*|e2m1| for codes 0..3
 constexpr uint32_t LUT_HI = 0x0C080604u;  // 2*|e2m1| for codes 4..7
+constexpr uint32_t POS_LO = 0x04030200u;  // v + 1 (0 for v = 0): looked up by non-negative elements
+constexpr uint32_t POS_HI = 0x0D090705u;
+constexpr uint32_t NEG_LO = 0xFDFEFF00u;  // -v: looked up by negative elements (sign bit flipped first)
+constexpr uint32_t NEG_HI = 0xF4F8FAFCu;
 
-// Exact dot product of 8 e2m1 elements (one 32-bit word of A) with 8 int8 values (x0,x1 = 2*x; n0,n1 = -2*x).
-__device__ __forceinline__ int dot8(uint32_t w, uint32_t x0, uint32_t x1, uint32_t n0, uint32_t n1, int d) {
+// Exact dot product of 8 e2m1 elements (one 32-bit word of A) with 8 int8 values (x0, x1 = 2*x).
+__device__ __forceinline__ int dot8(uint32_t w, uint32_t x0, uint32_t x1, int d) {
     const uint32_t wn = w ^ 0x88888888u;
-    d = __dp4a((int)prmt(LUT_LO, LUT_HI, w), (int)x0, d);
-    d = __dp4a((int)prmt(LUT_LO, LUT_HI, w >> 16), (int)x1, d);
-    d = __dp4a((int)prmt(LUT_LO, LUT_HI, wn), (int)n0, d);
-    d = __dp4a((int)prmt(LUT_LO, LUT_HI, wn >> 16), (int)n1, d);
+    d = __dp4a((int)prmt(POS_LO, POS_HI, w), (int)x0, d);
+    d = __dp4a((int)prmt(POS_LO, POS_HI, w >> 16), (int)x1, d);
+    d = __dp4a((int)prmt(NEG_LO, NEG_HI, wn), (int)x0, d);
+    d = __dp4a((int)prmt(NEG_LO, NEG_HI, wn >> 16), (int)x1, d);
     return d;
 }
 
@@ -97,10 +104,9 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     const int K = p.K, M = p.M;
     const int kbs = K / 16;
     uint8_t* xs = smem;                                   // K int8: 2*x
-    uint8_t* xn = smem + K;                               // K int8: -2*x
-    float* sxs = reinterpret_cast<float*>(smem + 2 * K);  // K/16 floats: 0.25 * sfx
+    float* sxs = reinterpret_cast<float*>(smem + K);      // K/16 floats: 0.25 * sfx
     // ring: 1024-byte aligned (the swizzled scale slices need it)
-    uint8_t* ring = smem + (((smem_u32(smem) + 2 * K + kbs * 4 + 1023u) & ~1023u) - smem_u32(smem));
+    uint8_t* ring = smem + (((smem_u32(smem) + K + kbs * 4 + 1023u) & ~1023u) - smem_u32(smem));
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
@@ -195,7 +201,6 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t p0 = prmt(LUT_LO, LUT_HI, w), p1 = prmt(LUT_LO, LUT_HI, w >> 16);
                     const uint32_t q0 = prmt(LUT_LO, LUT_HI, wn), q1 = prmt(LUT_LO, LUT_HI, wn >> 16);
                     reinterpret_cast<uint2*>(xs)[w4] = make_uint2(__vsub4(p0, q0), __vsub4(p1, q1));
-                    reinterpret_cast<uint2*>(xn)[w4] = make_uint2(__vsub4(q0, p0), __vsub4(q1, p1));
                 }
                 for (int kb = threadIdx.x; kb < kbs; kb += CW * 32) {
                     const uint8_t b = sg[(size_t)(kb >> 2) * 512 + (kb & 3)];
@@ -244,8 +249,6 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         const int kg = k0 + kseg;
                         const uint4 xa = *reinterpret_cast<const uint4*>(xs + kg);
                         const uint4 xb = *reinterpret_cast<const uint4*>(xs + kg + 16);
-                        const uint4 na = *reinterpret_cast<const uint4*>(xn + kg);
-                        const uint4 nb = *reinterpret_cast<const uint4*>(xn + kg + 16);
                         const float2 sx = *reinterpret_cast<const float2*>(sxs + (kg >> 4));
 #pragma unroll
                         for (int rr = 0; rr < RPW; rr++) {
@@ -253,10 +256,10 @@ gemv_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                             const uint16_t sfw = *reinterpret_cast<const uint16_t*>(
                                 Ss + soff[rr] + sub * 16 * (TILED ? 128 : SF_SLOT));
                             const float2 sa = e4m3x2_to_float2(sfw);
-                            int d0 = dot8(av.x, xa.x, xa.y, na.x, na.y, 0);
-                            d0 = dot8(av.y, xa.z, xa.w, na.z, na.w, d0);
-                            int d1 = dot8(av.z, xb.x, xb.y, nb.x, nb.y, 0);
-                            d1 = dot8(av.w, xb.z, xb.w, nb.z, nb.w, d1);
+                            int d0 = dot8(av.x, xa.x, xa.y, 0);
+                            d0 = dot8(av.y, xa.z, xa.w, d0);
+                            int d1 = dot8(av.z, xb.x, xb.y, 0);
+                            d1 = dot8(av.w, xb.z, xb.w, d1);
                             acc[rr] = fmaf((float)d0, sa.x * sx.x, acc[rr]);
                             acc[rr] = fmaf((float)d1, sa.y * sx.y, acc[rr]);
                         }
@@ -288,7 +291,7 @@ static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
     const bool tiled = (p.M % 128 == 0);
     const int stage = tiled ? GemvStage<KC, true>::BYTES : GemvStage<KC, false>::BYTES;
-    const size_t smem = 2 * (size_t)p.K + (size_t)(p.K / 16) * 4 + 1024 + (size_t)STAGES * stage;
+    const size_t smem = (size_t)p.K + (size_t)(p.K / 16) * 4 + 1024 + (size_t)STAGES * stage;
     if (smem > 227 * 1024 - 256) return NVFP4_ERR_UNSUPPORTED;
     const int RB = (p.M + 127) / 128;
     const int Kb4 = (p.K / 16 + 3) / 4;
@@ -346,7 +349,7 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
     if (K % 64 != 0) return NVFP4_ERR_K_MULTIPLE;
     if (((uintptr_t)a | (uintptr_t)x | (uintptr_t)sfa_sw | (uintptr_t)sfx_sw) & 15) return NVFP4_ERR_ALIGN;
     if ((uintptr_t)c & 1) return NVFP4_ERR_ALIGN;
-    if (K > 65536) return NVFP4_ERR_UNSUPPORTED;  // the vector (int8, twice) must fit in shared memory beside the ring
+    if (K > 65536) return NVFP4_ERR_UNSUPPORTED;  // the vector (int8) must fit in shared memory beside the ring
     GemvParams p;
     p.a = (const uint8_t*)a; p.x = (const uint8_t*)x; p.sfa = (const uint8_t*)sfa_sw; p.sfx = (const uint8_t*)sfx_sw;
     p.c = (__half*)c; p.M = M; p.K = K; p.L = L; p.x_rows = x_rows; p.alpha = alpha;
@@ -373,6 +376,9 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
         case 11: return launch_gemv<8, 1024, 3, 2>(p, s);
         case 12: return launch_gemv<8, 2048, 2, 2>(p, s);
         case 13: return launch_gemv<16, 1024, 4, 1>(p, s);
+        case 14: return launch_gemv<8, 1024, 3, 3>(p, s);
+        case 15: return launch_gemv<8, 2048, 3, 2>(p, s);
+        case 16: return launch_gemv<8, 1024, 6, 2>(p, s);
         default: return launch_gemv<8, 1024, 4, 2>(p, s);
     }
 }

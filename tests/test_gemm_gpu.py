@@ -115,3 +115,41 @@ def test_gemm_bad_arguments():
     assert lib.nvfp4_gemm(p, p, p, p, p, 128, 64, 256, 1, 1.0, None) == -4     # N % 128
     assert lib.nvfp4_gemm(p, p, p, p, None, 128, 128, 256, 1, 1.0, None) == -1
     assert lib.nvfp4_dual_gemm(p, p, p, p, p, p, p, 0, 128, 256, 1, 1.0, None) == -2
+
+
+_PAIR_CHILD = r'''
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from _util import dual_oracle_args, gemm_oracle_args, out_np, to_device
+from eval_test_b200 import _lib, inputs, nvfp4_dual_gemm, nvfp4_gemm
+from oracle import nvfp4_oracle as O
+for (m, n, k, l) in [(256, 256, 256, 1), (384, 256, 512, 1), (512, 512, 512, 2), (1024, 768, 2048, 1)]:
+    d = to_device(inputs.gemm_reference_style(m, n, k, l, seed=5, device="cpu"))
+    nvfp4_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    assert np.array_equal(out_np(d[-1]).view(np.uint16), O.c_gemm(*gemm_oracle_args(d)).view(np.uint16)), (m, n, k, l)
+for (m, n, k, l) in [(256, 128, 256, 1), (384, 256, 512, 2)]:
+    d = to_device(inputs.dual_gemm_reference_style(m, n, k, l, seed=5, device="cpu"))
+    nvfp4_dual_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    got, want = out_np(d[-1]).astype(np.float32), O.c_dual_gemm(*dual_oracle_args(d)).astype(np.float32)
+    assert np.all(np.abs(got - want) <= 1e-3 + 1e-3 * np.abs(want)), (m, n, k, l)
+print("pair ok")
+'''
+
+
+def test_cta_pair_kernels_in_a_child_process():
+    """The cta_group::2 variants (opt-in through NVFP4_GEMM_PAIR=1, read once per process): one pair tile, ragged
+    M (the second CTA of the last row tile owns no rows), batches, several tiles per pair; GEMM bit-exact, dual
+    GEMM within the harness's tolerance."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, NVFP4_GEMM_PAIR="1")
+    res = subprocess.run([sys.executable, "-c", _PAIR_CHILD, root], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "pair ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
