@@ -204,4 +204,9 @@ bool pair_kernel_suits(int M, int N, int K, int L, bool dual, int dev);
 int launch_gemm_pair(bool dual, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                      cudaStream_t stream);
 
+// Cluster split-K kernel for few-tile, long-K shapes (gemm_splitk_sm100.cu).  splitk_factor() returns the cluster
+// size (2, 4, 8) or 0 when the persistent kernel should be used; maps with 128-row boxes.
+int splitk_factor(int M, int N, int K, int L, int dev);
+int launch_gemm_splitk(int S, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream);
+
 }  // namespace nvfp4

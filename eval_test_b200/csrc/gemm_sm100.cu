@@ -334,10 +334,17 @@ extern "C" int nvfp4_gemm(const void* a, const void* b, const void* sfa_sw, cons
     static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 0; }();
     const bool use_pair = pair_mode != 0 && N % 256 == 0 && M >= 256 &&
                           (pair_mode == 1 || pair_kernel_suits(M, N, K, L, false, dev));
+    // few tiles and a long K loop: split K across a cluster (NVFP4_GEMM_SPLITK=0 turns it off)
+    // (NVFP4_GEMM_SPLITK = 2, 4 or 8 forces that cluster size where the shape allows it: tuning aid)
+    static const int splitk_mode = [] { const char* e_ = getenv("NVFP4_GEMM_SPLITK"); return e_ ? atoi(e_) : -1; }();
+    int split = (splitk_mode != 0 && !use_pair) ? splitk_factor(M, N, K, L, dev) : 0;
+    if (splitk_mode >= 2 && !use_pair && (long)((M + 127) / 128) * (N / 128) * L * splitk_mode <= 2 * sm_count(dev) &&
+        K / BK >= splitk_mode)
+        split = splitk_mode;
     CUtensorMap ta, tb;
     rc = make_operand_tmap(&ta, a, M, K, L, 128);
     if (rc) return rc;
-    rc = make_operand_tmap(&tb, b, N, K, L, (wide && !use_pair) ? 256 : 128);
+    rc = make_operand_tmap(&tb, b, N, K, L, (wide && !use_pair && !split) ? 256 : 128);
     if (rc) return rc;
     GemmParams p;
     p.sfa = (const uint8_t*)sfa_sw; p.sfb = (const uint8_t*)sfb_sw; p.sfb2 = nullptr; p.c = (__half*)c;
@@ -349,6 +356,7 @@ extern "C" int nvfp4_gemm(const void* a, const void* b, const void* sfa_sw, cons
 #ifdef NVFP4_PROFILE
     { const char* e_ = getenv("NVFP4_PROF_PTR"); p.prof = e_ ? (unsigned long long*)strtoull(e_, nullptr, 0) : nullptr; }
 #endif
+    if (split) return launch_gemm_splitk(split, ta, tb, p, (cudaStream_t)stream);
     if (use_pair) return launch_gemm_pair(false, ta, tb, tb, p, (cudaStream_t)stream);
     if (wide) return launch_gemm<256, false, false, 4>(ta, tb, tb, p, (cudaStream_t)stream);
     return launch_gemm<128, false, false, 6>(ta, tb, tb, p, (cudaStream_t)stream);

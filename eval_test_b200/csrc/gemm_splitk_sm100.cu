@@ -1,0 +1,280 @@
+// NVFP4 GEMM for shapes with few output tiles and a long K loop (the skinny-M shapes of the reference's own
+// benchmark list, eval/nvfp4_gemm/benchmarks.txt:1-3): split K across a thread-block CLUSTER.
+//
+// With M = 128 and N = 7168 there are 56 tiles of 128 x 128 for 148 SMs, each CTA walks 64 K steps one after the
+// other and a single CTA cannot pull more than about 100-180 GB/s through its four stages: a long K loop on a
+// third of the machine.  Here the
+// S CTAs of a cluster (S = 2, 4 or 8) share ONE output tile: CTA r accumulates K steps [r*k/S, (r+1)*k/S) in its
+// own tensor memory, then the partial sums are reduced through distributed shared memory:
+//   * every CTA writes its fp32 partial tile (64 KB) to its own shared memory,
+//   * a cluster-scope mbarrier round tells every CTA that all partials are written,
+//   * CTA r reduces the column slice [r*128/S, (r+1)*128/S): each thread reads its row's slice from all S CTAs with
+//     ld.shared::cluster, adds them in rank order (deterministic), applies alpha, rounds to fp16 and stores.
+// No global scratch, no atomics.  One tile per cluster (the shapes this serves have fewer tiles than SMs).
+// Every mbarrier wait is bounded; the closing hardware cluster barrier is reached by every thread on every path.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "gemm_common.cuh"
+#include "nvfp4_internal.h"
+#include "ptx_sm100.cuh"
+
+namespace nvfp4 {
+
+constexpr int SK_BN = 128;
+constexpr int SK_STAGES = 4;
+constexpr uint32_t SK_A_BYTES = 128 * 128, SK_B_BYTES = 128 * 128, SK_SF_BYTES = 2048;
+constexpr uint32_t SK_STAGE_BYTES = SK_A_BYTES + SK_B_BYTES + 2 * SK_SF_BYTES;
+constexpr uint32_t SK_RED_BYTES = 128 * SK_BN * 4;   // fp32 partial tile
+constexpr size_t SK_SMEM = SK_STAGES * SK_STAGE_BYTES + SK_RED_BYTES + 1024;
+
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                 : "r"(cluster_addr)
+                 : "memory");
+    return v;
+}
+
+template <int S>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                   const GemmParams p) {
+    constexpr int STAGES = SK_STAGES;
+    constexpr uint32_t TCOLS = 256;                    // accumulator 128 columns + scales 2 x 32
+    constexpr uint32_t SF_BASE = 128;
+    constexpr int SLICE = SK_BN / S;                   // output columns this CTA reduces
+    static_assert(S == 2 || S == 4 || S == 8, "cluster size");
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 2];
+    __shared__ uint32_t tmem_base_slot;
+
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t red0 = smem0 + STAGES * SK_STAGE_BYTES;     // same offset in every CTA of the cluster
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full = smem_u32(&bars[2 * STAGES]);
+    const uint32_t red_ready = acc_full + 8;                   // 4 epilogue warps of each of the S CTAs
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(acc_full, 1);
+        mbar_init(red_ready, 4 * S);
+        fence_mbar_init();
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&tmem_base_slot), TCOLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();     // every CTA's barriers exist before a peer arrives on them
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    // tile of this cluster, K range of this CTA
+    const int tiles_m = (p.M + BM - 1) / BM, tiles_n = p.N / SK_BN;
+    const int t = blockIdx.x / S;
+    const int l = t / (tiles_m * tiles_n);
+    const int r_ = t - l * tiles_m * tiles_n;
+    const int nt = r_ / tiles_m, mt = r_ - nt * tiles_m;       // row tiles of one column tile run together
+    const int m0 = mt * BM, n0 = nt * SK_BN;
+    const int kiters_all = p.K / BK;
+    const int kbase = kiters_all / S, krem = kiters_all % S;
+    const int kcount = kbase + ((int)rank < krem ? 1 : 0);
+    const int kfirst = (int)rank * kbase + min((int)rank, krem);
+    const size_t sf_row_block = (size_t)(p.K / 64) * 512;
+    const uint8_t* sfa_t = p.sfa + ((size_t)l * tiles_m + mt) * sf_row_block;
+    const uint8_t* sfb_t = p.sfb + ((size_t)l * tiles_n + nt) * sf_row_block;
+
+    if (warp == 0) {
+        if (elect_one()) {
+            for (int it = 0; it < kcount; it++) {
+                const int slot = it % STAGES;
+                if (!mbar_wait(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns)) {
+                    report_status(p.status, DEV_TIMEOUT_PRODUCER);
+                    break;
+                }
+                const uint32_t full = full0 + 8 * slot;
+                const uint32_t sA = smem0 + slot * SK_STAGE_BYTES, sB = sA + SK_A_BYTES;
+                const uint32_t sSFA = sB + SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
+                const int k0 = (kfirst + it) * BK;
+                mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
+                tma_load_3d(sA, &tmap_a, k0, m0, l, full);
+                tma_load_3d(sB, &tmap_b, k0, n0, l, full);
+                const size_t koff = (size_t)(k0 / 64) * 512;
+                bulk_g2s(sSFA, sfa_t + koff, 2048u, full);
+                bulk_g2s(sSFB, sfb_t + koff, 2048u, full);
+            }
+        }
+    } else if (warp == 1) {
+        if (elect_one()) {
+            constexpr uint32_t idesc = make_idesc_nvfp4(BM, SK_BN);
+            bool alive = true;
+            for (int it = 0; it < kcount; it++) {
+                const int slot = it % STAGES;
+                if (!mbar_wait(full0 + 8 * slot, (it / STAGES) & 1, p.budget_ns)) {
+                    report_status(p.status, DEV_TIMEOUT_CONSUMER);
+                    alive = false;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t sA = smem0 + slot * SK_STAGE_BYTES, sB = sA + SK_A_BYTES;
+                const uint32_t sSFA = sB + SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
+                const uint32_t t_sfa = tmem_base + SF_BASE + (it & 1) * 32, t_sfb = t_sfa + 16;
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++) {
+                    tc_cp_sf_atom(t_sfa + 4 * ks, make_desc_sf(sSFA + 512 * ks));
+                    tc_cp_sf_atom(t_sfb + 4 * ks, make_desc_sf(sSFB + 512 * ks));
+                }
+#pragma unroll
+                for (int ks = 0; ks < 4; ks++)
+                    tc_mma_nvfp4(tmem_base, make_desc_k_sw128(sA + 32 * ks), make_desc_k_sw128(sB + 32 * ks), idesc,
+                                 t_sfa + 4 * ks, t_sfb + 4 * ks, (it | ks) != 0 ? 1u : 0u);
+                tc_commit(empty0 + 8 * slot);
+            }
+            if (alive) tc_commit(acc_full);
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue warps: partial -> smem -> reduce
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        bool ok = mbar_wait(acc_full, 0, p.budget_ns);
+        if (!ok && lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
+        if (ok) {
+            tc_fence_after_sync();
+            const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
+            // partial tile layout: 16-byte chunk c4 of row r at (c4 * 128 + r) * 16 -> consecutive lanes,
+            // consecutive addresses, for the writes here and for the (remote) reads below
+            uint8_t* red_local = smem_raw + (red0 - smem_u32(smem_raw));
+#pragma unroll
+            for (int cc = 0; cc < SK_BN / 32; cc++) {
+                uint32_t v[32];
+                tc_ld_32x32(t_lane + cc * 32, v);
+                tc_wait_ld();
+#pragma unroll
+                for (int j = 0; j < 8; j++)
+                    *reinterpret_cast<uint4*>(red_local + ((size_t)((cc * 8 + j) * 128 + row_in_tile)) * 16) =
+                        make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+        }
+        // tell every CTA of the cluster (this one included) that this warp's rows are written; a warp whose
+        // accumulator never completed still arrives, so that no peer waits for it in vain
+        __syncwarp();
+        if (lane == 0) {
+#pragma unroll
+            for (int c = 0; c < S; c++) mbar_arrive_cluster(mapa_shared(red_ready, (uint32_t)c));
+        }
+        if (ok) {
+            ok = mbar_wait_cluster(red_ready, 0, p.budget_ns);
+            if (!ok && lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
+        }
+        if (ok) {
+            const int row = m0 + row_in_tile;
+            float acc[SLICE];
+#pragma unroll
+            for (int i = 0; i < SLICE; i++) acc[i] = 0.f;
+#pragma unroll
+            for (int c = 0; c < S; c++) {
+                const uint32_t peer = mapa_shared(red0, (uint32_t)c);
+#pragma unroll
+                for (int j = 0; j < SLICE / 4; j++) {
+                    const int c4 = (int)rank * (SLICE / 4) + j;
+                    const float4 v = ld_cluster_f4(peer + (uint32_t)((c4 * 128 + row_in_tile) * 16));
+                    acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
+                }
+            }
+            if (row < p.M) {
+                __half* dst = p.c + ((size_t)l * p.M + row) * p.N + n0 + (int)rank * SLICE;
+                uint32_t o[SLICE / 2];
+#pragma unroll
+                for (int i = 0; i < SLICE / 2; i++) {
+                    __half2 h = __floats2half2_rn(p.alpha * acc[2 * i], p.alpha * acc[2 * i + 1]);
+                    o[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+#pragma unroll
+                for (int i = 0; i < SLICE / 16; i++) {
+                    const uint32_t w8[8] = {o[8 * i], o[8 * i + 1], o[8 * i + 2], o[8 * i + 3],
+                                            o[8 * i + 4], o[8 * i + 5], o[8 * i + 6], o[8 * i + 7]};
+                    st_global_256(dst + 16 * i, w8);
+                }
+            }
+        }
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();     // no CTA exits (or frees its shared memory) while a peer may still read its partial tile
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, TCOLS);
+    }
+}
+
+// ------------------------------------------------------------------------------------------ host side
+namespace {
+
+template <int S>
+int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles, cudaStream_t stream) {
+    static bool done[64] = {};
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
+    if (!done[dev]) {
+        e = cudaFuncSetAttribute(gemm_splitk_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM);
+        if (e != cudaSuccess) return (int)e;
+        done[dev] = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles * S);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = SK_SMEM;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = S; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<S>, ta, tb, p);
+    return e == cudaSuccess ? NVFP4_OK : (int)e;
+}
+
+}  // namespace
+
+// Cluster size to split K with, or 0 when the shape is better served by the persistent kernel.
+// Measured on B200 (device time per call, CUDA-graph replay): the reduction through distributed shared memory
+// costs about 3 us, a K step about 0.2 us, so splitting pays only for long K loops - M=128 N=7168 K=16384:
+// 16.4 us unsplit, 14.2 us with S=2; M=128 N=4096 K=7168: 9.6 / 9.5 / 9.4 us for S = 1 / 2 / 4; K=2048: 5.6 us
+// unsplit, 7.2 us with S=2.  Hence: at most half the SMs busy without splitting, and at least 16 K steps per CTA.
+int splitk_factor(int M, int N, int K, int L, int dev) {
+    const long tiles = (long)((M + BM - 1) / BM) * (N / SK_BN) * L;
+    const int kiters = K / BK;
+    const int sms = sm_count(dev);
+    if (tiles <= 0 || tiles * 2 > sms) return 0;
+    for (int s = 4; s >= 2; s /= 2)
+        if (tiles * s <= sms && kiters / s >= 16) return s;
+    return 0;
+}
+
+int launch_gemm_splitk(int S, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
+    const int tiles = ((p.M + BM - 1) / BM) * (p.N / SK_BN) * p.L;
+    switch (S) {
+        case 2: return launch_splitk<2>(ta, tb, p, tiles, stream);
+        case 4: return launch_splitk<4>(ta, tb, p, tiles, stream);
+        case 8: return launch_splitk<8>(ta, tb, p, tiles, stream);
+        default: return NVFP4_ERR_INTERNAL;
+    }
+}
+
+}  // namespace nvfp4

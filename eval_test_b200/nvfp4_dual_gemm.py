@@ -18,14 +18,18 @@ def compile_kernel():
 
 def custom_kernel(data, alpha: float = 1.0):
     a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, c = data
-    m, k2, l = a.shape
-    n = b1.shape[0]
-    k = 2 * k2
-    with torch.cuda.device(a.device):
-        code = _lib.load().nvfp4_dual_gemm(
+    tensors = (a, b1, b2, sfa_p, sfb1_p, sfb2_p, c)
+    ent = _args.lookup(data, tensors)
+    if ent is None:
+        m, k2, l = a.shape
+        n = b1.shape[0]
+        k = 2 * k2
+        ent = _args.remember(data, tensors, (
             _args.operand_ptr(a, m, k2, l, "a"), _args.operand_ptr(b1, n, k2, l, "b1"),
             _args.operand_ptr(b2, n, k2, l, "b2"), _args.scales_ptr(sfa_p, m, k, l, "sfa_permuted"),
             _args.scales_ptr(sfb1_p, n, k, l, "sfb1_permuted"), _args.scales_ptr(sfb2_p, n, k, l, "sfb2_permuted"),
-            _args.output_ptr(c, m, n, l), m, n, k, l, float(alpha), _args.stream_ptr(a.device))
-    _lib.check(code, "nvfp4_dual_gemm")
+            _args.output_ptr(c, m, n, l), m, n, k, l))
+    code = _args.launch(_lib.load().nvfp4_dual_gemm, ent, float(alpha))
+    if code:
+        _lib.check(code, "nvfp4_dual_gemm")
     return c

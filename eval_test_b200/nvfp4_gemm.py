@@ -19,13 +19,17 @@ def compile_kernel():
 
 def custom_kernel(data, alpha: float = 1.0):
     a, b, _, _, sfa_p, sfb_p, c = data
-    m, k2, l = a.shape
-    n = b.shape[0]
-    k = 2 * k2
-    with torch.cuda.device(a.device):
-        code = _lib.load().nvfp4_gemm(
+    tensors = (a, b, sfa_p, sfb_p, c)
+    ent = _args.lookup(data, tensors)
+    if ent is None:
+        m, k2, l = a.shape
+        n = b.shape[0]
+        k = 2 * k2
+        ent = _args.remember(data, tensors, (
             _args.operand_ptr(a, m, k2, l, "a"), _args.operand_ptr(b, n, k2, l, "b"),
             _args.scales_ptr(sfa_p, m, k, l, "sfa_permuted"), _args.scales_ptr(sfb_p, n, k, l, "sfb_permuted"),
-            _args.output_ptr(c, m, n, l), m, n, k, l, float(alpha), _args.stream_ptr(a.device))
-    _lib.check(code, "nvfp4_gemm")
+            _args.output_ptr(c, m, n, l), m, n, k, l))
+    code = _args.launch(_lib.load().nvfp4_gemm, ent, float(alpha))
+    if code:
+        _lib.check(code, "nvfp4_gemm")
     return c

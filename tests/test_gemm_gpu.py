@@ -153,3 +153,51 @@ def test_cta_pair_kernels_in_a_child_process():
     env = dict(os.environ, NVFP4_GEMM_PAIR="1")
     res = subprocess.run([sys.executable, "-c", _PAIR_CHILD, root], env=env, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0 and "pair ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+_SPLITK_CHILD = r'''
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from _util import gemm_oracle_args, out_np, to_device
+from eval_test_b200 import _lib, check, inputs, nvfp4_gemm
+from oracle import nvfp4_oracle as O
+for (m, n, k, l) in [(128, 1536, 7168, 1), (200, 512, 1792, 2), (128, 128, 4096, 1), (384, 256, 2560, 1)]:
+    d = to_device(inputs.gemm_reference_style(m, n, k, l, seed=77, device="cpu"))
+    nvfp4_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    assert np.array_equal(out_np(d[-1]).view(np.uint16), O.c_gemm(*gemm_oracle_args(d)).view(np.uint16)), (m, n, k, l)
+d = to_device(inputs.gemm_quantized(128, 1024, 4096, 1, seed=9, device="cpu"))
+nvfp4_gemm.custom_kernel(d, alpha=0.5)
+torch.cuda.synchronize()
+got, want = torch.from_numpy(out_np(d[-1])), torch.from_numpy(O.c_gemm(*gemm_oracle_args(d), 0.5))
+assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+print("splitk ok")
+'''
+
+
+@pytest.mark.parametrize("cluster", [2, 4, 8])
+def test_gemm_cluster_split_k_in_a_child_process(cluster):
+    """The cluster split-K kernel with every cluster size (forced through NVFP4_GEMM_SPLITK, read once per
+    process): dyadic inputs must match the oracle bit for bit (the partial sums and their rank-ordered reduction
+    are exact), including an uneven split of the K steps (7 or 10 steps), ragged M and batches; a quantised case
+    within the harness's tolerance."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, NVFP4_GEMM_SPLITK=str(cluster))
+    res = subprocess.run([sys.executable, "-c", _SPLITK_CHILD, root], env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert res.returncode == 0 and "splitk ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_gemm_long_k_takes_split_k_by_default(oracle):
+    """M = 128, N = 7168, K = 16384 (the reference's first benchmark shape) is split across clusters of 2 by the
+    default heuristic."""
+    from eval_test_b200 import inputs
+    data = to_device(inputs.gemm_reference_style(128, 7168, 16384, 1, seed=1111, device="cpu"))
+    got, want = _gemm(data), oracle.c_gemm(*gemm_oracle_args(data))
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
