@@ -13,7 +13,7 @@ HEADER = _PKG.parent / "include" / "nvfp4_b200.h"
 
 NVCC_FLAGS = [
     "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
-    "--use_fast_math", "-Xcompiler", "-fPIC", "-shared", "--cudart=static",
+    "-Xcompiler", "-fPIC", "-shared", "--cudart=static",
 ]
 
 
@@ -69,11 +69,12 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_dual_gemm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp]
     lib.nvfp4_grouped_gemm.argtypes = [ctypes.POINTER(Group), i, f, vp]
     lib.nvfp4_grouped_gemm_noalloc.argtypes = [ctypes.POINTER(Group), i, f, vp]
+    lib.nvfp4_quantize_f32.argtypes = [vp, vp, vp, i, i, i, vp]
     lib.nvfp4_device_status.argtypes = [i, i]
     lib.nvfp4_wait_selftest.argtypes = [i, ctypes.POINTER(ctypes.c_double), vp]
     lib.nvfp4_strerror.argtypes = [i]
     lib.nvfp4_strerror.restype = ctypes.c_char_p
-    for name in ("nvfp4_gemv", "nvfp4_gemm", "nvfp4_dual_gemm", "nvfp4_grouped_gemm", "nvfp4_grouped_gemm_noalloc", "nvfp4_device_status",
+    for name in ("nvfp4_gemv", "nvfp4_gemm", "nvfp4_dual_gemm", "nvfp4_grouped_gemm", "nvfp4_grouped_gemm_noalloc", "nvfp4_quantize_f32", "nvfp4_device_status",
                  "nvfp4_wait_selftest", "nvfp4_abi_version"):
         getattr(lib, name).restype = i
     _lib = lib

@@ -80,7 +80,9 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
     return tc;
 }
 
-__device__ __forceinline__ float silu_mul(float x, float y) { return x / (1.0f + __expf(-x)) * y; }
+// silu(x) * y with the fast exponential and the approximate (2 ulp) division: an IEEE division here made the dual
+// GEMM's epilogue three times longer than its main loop; the result is rounded to fp16 anyway.
+__device__ __forceinline__ float silu_mul(float x, float y) { return __fdividef(x, 1.0f + __expf(-x)) * y; }
 
 // Tile t of a plain / dual GEMM (all batches share the maps; the batch is the third TMA coordinate) or of a
 // grouped GEMM (binary search of the group whose tile range holds t; row-tile index fastest inside a group,

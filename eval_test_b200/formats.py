@@ -42,13 +42,14 @@ def quantize_nvfp4(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """fp32 ``[..., K]`` -> (packed e2m1 ``[..., K/2]`` uint8, e4m3fn scale bits ``[..., K/16]`` uint8).
 
     Per 16-element block: scale = amax/6 rounded to e4m3 (RNE, clamped to 448), values = RNE(x / scale) on
-    the e2m1 grid; a zero scale gives zero values.
+    the e2m1 grid; a zero scale gives zero values.  amax/6 is computed as amax * fl32(1/6), the same on CPU, on
+    CUDA (where torch turns a division by a scalar into this product anyway) and in ``nvfp4_quantize_f32``.
     """
     K = x.shape[-1]
     assert K % SF_VEC == 0
     xb = x.float().reshape(*x.shape[:-1], K // SF_VEC, SF_VEC)
     amax = xb.abs().amax(dim=-1)
-    sf = (amax / E2M1_MAX).clamp(max=E4M3_MAX).to(torch.float8_e4m3fn)
+    sf = (amax * (1.0 / E2M1_MAX)).clamp(max=E4M3_MAX).to(torch.float8_e4m3fn)
     s32 = sf.float().unsqueeze(-1)
     y = torch.where(s32 > 0, xb / s32, torch.zeros_like(xb))
     codes = round_to_e2m1_code(y).reshape(*x.shape[:-1], K)
