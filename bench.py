@@ -326,8 +326,66 @@ class GroupedGemmWorkload:
         return O.c_grouped_gemm(args)
 
 
+class QuantizeWorkload:
+    """fp32 -> NVFP4 quantiser in front of the path: one 16384 x 16384 fp32 operand per step (HBM-bound:
+    4 bytes read, 0.5 + 1/16 bytes written per element).  N > 1: every rank quantises its own operand (weak)."""
+    name = "quantize_f32_16384x16384"
+    metric = "nvfp4_quantize_hbm_gbs"
+    unit, per = "GB/s", 1e9
+    dtype = "fp32 in, e2m1 + e4m3 block scales out"
+    bound, kernel, scaling = "hbm", "quantize_f32_kernel", "weak"
+
+    def __init__(self, rows=16384, k=16384):
+        self.rows, self.k = rows, k
+
+    def small(self):
+        return QuantizeWorkload(rows=4096)
+
+    def work(self, world=1, rows=None) -> int:
+        rows = self.rows if rows is None else rows
+        return rows * self.k * 4 + rows * self.k // 2 + rows * self.k // 16
+
+    def job(self, world=1) -> int:
+        return self.work() * world
+
+    def make(self, rank, world, device):
+        import torch
+        g = torch.Generator(device=device).manual_seed(rank)
+        x = torch.randn((1, self.rows, self.k), generator=g, device=device)
+        return [x, None]
+
+    def run(self, data):
+        from eval_test_b200 import quantize
+        data[1] = quantize.quantize_operand(data[0])
+        return data[1]
+
+    def io(self, data):
+        op, _, sf_p = data[1] if data[1] is not None else self.run(data)
+        return [data[0]], [op, sf_p]
+
+    def with_inputs(self, data, moved):
+        return [moved[0], None]
+
+    def config(self, world):
+        return {"workload": self.name, "rows": self.rows, "k": self.k, "sharding": "one operand per rank",
+                "l2": "1 GiB input larger than L2 (126 MB)", "generator": "N(0,1), seed = rank"}
+
+    def cpu_sample(self, data, rows=1024):
+        x = data[0][:, :rows].cpu()
+        return (x,), self.work(rows=rows), f"rows 0..{rows - 1} (torch CPU ops, formats.quantize_nvfp4 + swizzle)"
+
+    def cpu_data(self, rows=1024):
+        import torch
+        return [torch.randn((1, rows, self.k), generator=torch.Generator().manual_seed(0)), None]
+
+    def cpu_run(self, args):
+        from eval_test_b200 import formats as F
+        packed, sf = F.quantize_nvfp4(args[0])
+        return packed, F.swizzle_scales(sf)
+
+
 WORKLOADS = {"gemv": GemvWorkload, "gemm": GemmWorkload, "dual_gemm": DualGemmWorkload,
-             "grouped_gemm": GroupedGemmWorkload}
+             "grouped_gemm": GroupedGemmWorkload, "quantize": QuantizeWorkload}
 
 
 # ----------------------------------------------------------------------------------------------- clocks
@@ -510,14 +568,15 @@ def main():
     # ---- end to end: pinned host inputs -> device, kernel, outputs -> host, every step ----
     def flat(t):
         """All elements of a dense (possibly permuted) tensor as one 1-D view over its memory."""
-        return torch.as_strided(t if t.dtype == torch.float16 else t.view(torch.uint8), (t.numel(),), (1,),
-                                t.storage_offset())
+        if t.element_size() == 1:
+            t = t.view(torch.uint8)
+        return torch.as_strided(t, (t.numel(),), (1,), t.storage_offset())
 
     ins, outs = wl.io(data)
-    host_in = [torch.empty(t.numel(), dtype=torch.uint8).pin_memory() for t in ins]
+    host_in = [torch.empty(t.numel(), dtype=flat(t).dtype).pin_memory() for t in ins]
     for h, t in zip(host_in, ins):
         h.copy_(flat(t))
-    host_out = [torch.empty(o.numel(), dtype=o.dtype).pin_memory() for o in outs]
+    host_out = [torch.empty(o.numel(), dtype=flat(o).dtype).pin_memory() for o in outs]
     dev_in = [torch.empty_like(t) for t in ins]
     for d, t in zip(dev_in, ins):
         assert d.stride() == t.stride()
@@ -529,7 +588,7 @@ def main():
         for d, h in zip(dev_in, host_in):
             flat(d).copy_(h, non_blocking=True)
         wl.run(e2e_data)
-        for h, o in zip(host_out, outs):
+        for h, o in zip(host_out, wl.io(e2e_data)[1]):
             h.copy_(flat(o), non_blocking=True)
 
     e2e_steps = 1 if args.small else args.e2e_steps

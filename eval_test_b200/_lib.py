@@ -12,7 +12,7 @@ SO_PATH = _PKG / "libnvfp4_b200.so"
 HEADER = _PKG.parent / "include" / "nvfp4_b200.h"
 
 NVCC_FLAGS = [
-    "-O3", "-std=c++17", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
+    "-O3", "-std=c++17", "--threads", "4", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-shared", "--cudart=static",
 ]
 

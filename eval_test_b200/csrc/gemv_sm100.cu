@@ -363,28 +363,11 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
     if (K > 32768) return launch_gemv<8, 1024, 3>(p, s);
     if (K > 16384) return launch_gemv<8, 2048, 4>(p, s);
     switch (variant) {  // tuning knob; 0 is the shipped configuration
-        case 1: return launch_gemv<16, 2048, 5>(p, s);
-        case 2: return launch_gemv<8, 4096, 2>(p, s);
-        case 3: return launch_gemv<8, 1024, 4, 2>(p, s);
-        case 4: return launch_gemv<16, 1024, 8>(p, s);
-        case 5: return launch_gemv<8, 1024, 8>(p, s);
-        case 6: return launch_gemv<8, 2048, 5, 1, 1>(p, s);   // no arithmetic: copy pipeline alone
-        case 7: return launch_gemv<8, 4096, 2, 1, 1>(p, s);
-        case 8: return launch_gemv<8, 1024, 4, 2, 1>(p, s);
-        case 9: return launch_gemv<16, 4096, 2>(p, s);
-        case 10: return launch_gemv<8, 1024, 5, 2>(p, s);
-        case 11: return launch_gemv<8, 1024, 3, 2>(p, s);
-        case 12: return launch_gemv<8, 1024, 4, 2>(p, s);
-        case 13: return launch_gemv<16, 1024, 4, 1>(p, s);
-        case 14: return launch_gemv<8, 1024, 3, 3>(p, s);
-        case 15: return launch_gemv<8, 2048, 3, 2>(p, s);
-        case 16: return launch_gemv<8, 1024, 6, 2>(p, s);
-        case 17: return launch_gemv<16, 1024, 4, 2>(p, s);
-        case 18: return launch_gemv<16, 2048, 2, 2>(p, s);
-        case 19: return launch_gemv<16, 1024, 3, 2>(p, s);
-        case 20: return launch_gemv<4, 1024, 3, 3>(p, s);
-        case 21: return launch_gemv<4, 2048, 2, 3>(p, s);
-        case 22: return launch_gemv<4, 1024, 4, 4>(p, s);
+        case 1: return launch_gemv<8, 1024, 4, 2>(p, s);
+        case 2: return launch_gemv<8, 2048, 5, 1>(p, s);
+        case 3: return launch_gemv<16, 2048, 5, 1>(p, s);
+        case 6: return launch_gemv<8, 2048, 2, 2, 1>(p, s);   // no arithmetic: the copy pipeline alone
         default: return launch_gemv<8, 2048, 2, 2>(p, s);
     }
+
 }

@@ -29,7 +29,7 @@ def round_to_e2m1_code(y: torch.Tensor) -> torch.Tensor:
     code = ((m > 0.25).to(torch.uint8) + (m >= 0.75).to(torch.uint8) + (m > 1.25).to(torch.uint8)
             + (m >= 1.75).to(torch.uint8) + (m > 2.5).to(torch.uint8) + (m >= 3.5).to(torch.uint8)
             + (m > 5.0).to(torch.uint8))
-    sign = ((y < 0) & (code > 0)).to(torch.uint8) << 3
+    sign = torch.signbit(y).to(torch.uint8) << 3   # a negative value that rounds to zero keeps its sign (-0)
     return code | sign
 
 
@@ -42,8 +42,9 @@ def quantize_nvfp4(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     """fp32 ``[..., K]`` -> (packed e2m1 ``[..., K/2]`` uint8, e4m3fn scale bits ``[..., K/16]`` uint8).
 
     Per 16-element block: scale = amax/6 rounded to e4m3 (RNE, clamped to 448), values = RNE(x / scale) on
-    the e2m1 grid; a zero scale gives zero values.  amax/6 is computed as amax * fl32(1/6), the same on CPU, on
-    CUDA (where torch turns a division by a scalar into this product anyway) and in ``nvfp4_quantize_f32``.
+    the e2m1 grid; a zero scale gives zero values.  Both divisions are done as products with a correctly rounded
+    fp32 reciprocal - amax * fl32(1/6) and x * fl32(1/scale) - which gives the same bits on CPU, on CUDA and in
+    the ``nvfp4_quantize_f32`` kernel (where an IEEE division per element would make the kernel compute-bound).
     """
     K = x.shape[-1]
     assert K % SF_VEC == 0
@@ -51,7 +52,7 @@ def quantize_nvfp4(x: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
     amax = xb.abs().amax(dim=-1)
     sf = (amax * (1.0 / E2M1_MAX)).clamp(max=E4M3_MAX).to(torch.float8_e4m3fn)
     s32 = sf.float().unsqueeze(-1)
-    y = torch.where(s32 > 0, xb / s32, torch.zeros_like(xb))
+    y = torch.where(s32 > 0, xb * torch.reciprocal(s32), torch.zeros_like(xb))
     codes = round_to_e2m1_code(y).reshape(*x.shape[:-1], K)
     return pack_e2m1(codes), sf.view(torch.uint8)
 
