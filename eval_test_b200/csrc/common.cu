@@ -55,6 +55,15 @@ int* status_word_if_allocated(int dev) {
     return g_status_dev[dev];
 }
 
+void free_status_words() {
+    std::lock_guard<std::mutex> lk(g_mu);
+    for (int dev = 0; dev < MAX_DEV; dev++) {
+        if (g_status_host[dev]) cudaFreeHost(g_status_host[dev]);
+        g_status_host[dev] = nullptr;
+        g_status_dev[dev] = nullptr;
+    }
+}
+
 unsigned long long wait_budget_ns() {
     static unsigned long long v = [] {
         const char* e = getenv("NVFP4_WAIT_BUDGET_MS");

@@ -532,6 +532,33 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
 
+// Frees what the library allocated on first use: the grouped-GEMM problem tables of every device (pinned staging,
+// device tables, events) and the status words.  The caller must have synchronised the streams it used.
+namespace nvfp4 {
+void free_status_words();
+}
+extern "C" int nvfp4_shutdown(void) {
+    std::lock_guard<std::mutex> lk(g_table_mu);
+    int cur = 0;
+    if (cudaGetDevice(&cur) != cudaSuccess) return NVFP4_ERR_INTERNAL;
+    for (int dev = 0; dev < 64; dev++) {
+        bool any = false;
+        for (const TableSlot& sl : g_rings[dev].slots) any = any || sl.host || sl.dev || sl.done;
+        if (!any) continue;
+        cudaSetDevice(dev);
+        for (TableSlot& sl : g_rings[dev].slots) {
+            if (sl.host) cudaFreeHost(sl.host);
+            if (sl.dev) cudaFree(sl.dev);
+            if (sl.done) cudaEventDestroy(sl.done);
+            sl = TableSlot();
+        }
+        g_rings[dev].next = 0;
+    }
+    cudaSetDevice(cur);
+    free_status_words();
+    return NVFP4_OK;
+}
+
 // ------------------------------------------------------------------------------------------ grouped GEMM, no allocation
 // Some callers cannot let this library allocate: a serving process whose own allocator has already claimed
 // all of HBM (a cudaMalloc from a library would fail, or would have to be carved out of the budget up front),

@@ -111,6 +111,11 @@ int nvfp4_device_status(int dev, int clear);
  * No counterpart in the reference. */
 int nvfp4_wait_selftest(int budget_ms, double* elapsed_ms, void* stream);
 
+/* Frees the memory the library allocated on first use (grouped-GEMM problem tables, status words).  Synchronise
+ * the streams first; later calls allocate again.  The reference frees per call instead (eight cudaMalloc /
+ * cudaFree pairs in grouped_gemm_launch, eval/nvfp4_grouped_gemm/submission.py:1111-1152). */
+int nvfp4_shutdown(void);
+
 /* Text for any value returned by the functions above or by nvfp4_device_status(). */
 const char* nvfp4_strerror(int code);
 
