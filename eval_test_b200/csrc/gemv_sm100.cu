@@ -349,13 +349,18 @@ extern "C" int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, cons
     if (K % 64 != 0) return NVFP4_ERR_K_MULTIPLE;
     if (((uintptr_t)a | (uintptr_t)x | (uintptr_t)sfa_sw | (uintptr_t)sfx_sw) & 15) return NVFP4_ERR_ALIGN;
     if ((uintptr_t)c & 1) return NVFP4_ERR_ALIGN;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    // Default: the tensor-core streaming kernel.  NVFP4_GEMV_PATH=alu selects the kernel of this file (decode on
+    // the CUDA cores), read on every call so that one process can compare the two.
+    const char* path = getenv("NVFP4_GEMV_PATH");
+    if (!(path && path[0] == 'a'))
+        return launch_gemv_tc(a, x, sfa_sw, sfx_sw, c, M, K, L, x_rows, alpha, dev, (cudaStream_t)stream);
     if (K > 65536) return NVFP4_ERR_UNSUPPORTED;  // the vector (int8) must fit in shared memory beside the ring
     GemvParams p;
     p.a = (const uint8_t*)a; p.x = (const uint8_t*)x; p.sfa = (const uint8_t*)sfa_sw; p.sfx = (const uint8_t*)sfx_sw;
     p.c = (__half*)c; p.M = M; p.K = K; p.L = L; p.x_rows = x_rows; p.alpha = alpha;
-    int dev = 0;
-    cudaError_t e = cudaGetDevice(&dev);
-    if (e != cudaSuccess) return (int)e;
     p.status = status_word(dev);
     p.budget_ns = wait_budget_ns();
     cudaStream_t s = (cudaStream_t)stream;

@@ -21,4 +21,8 @@ unsigned long long wait_budget_ns();
 int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const void* base, const uint64_t* dims,
                  const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle);
 
+// Tensor-core streaming GEMV (gemv_tc_sm100.cu); arguments as nvfp4_gemv, already validated.
+int launch_gemv_tc(const void* a, const void* x, const void* sfa_sw, const void* sfx_sw, void* c, int M, int K, int L,
+                   int x_rows, float alpha, int dev, cudaStream_t stream);
+
 }  // namespace nvfp4

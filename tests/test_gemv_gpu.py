@@ -12,6 +12,16 @@ REFERENCE_TESTS = [(128, 256, 1), (128, 1536, 1), (128, 3072, 1), (256, 7168, 1)
                    (384, 7168, 2), (512, 512, 2), (512, 4096, 2), (512, 1536, 2)]
 
 
+@pytest.fixture(params=["tensor", "alu"])
+def path(request, monkeypatch):
+    """Both GEMV kernels: the tensor-core stream (default) and the decode-on-CUDA-cores kernel."""
+    if request.param == "alu":
+        monkeypatch.setenv("NVFP4_GEMV_PATH", "alu")
+    else:
+        monkeypatch.delenv("NVFP4_GEMV_PATH", raising=False)
+    return request.param
+
+
 def _run(data, alpha=1.0):
     from eval_test_b200 import _lib, nvfp4_gemv
     out = nvfp4_gemv.custom_kernel(data, alpha=alpha) if alpha != 1.0 else nvfp4_gemv.custom_kernel(data)
@@ -27,15 +37,16 @@ def _oracle(oracle, data, alpha=1.0):
 
 
 @pytest.mark.parametrize("m,k,l", REFERENCE_TESTS)
-def test_reference_style_bit_exact(oracle, m, k, l):
+def test_reference_style_bit_exact(oracle, path, m, k, l):
     from eval_test_b200 import inputs
     data = to_device(inputs.gemv_reference_style(m, k, l, seed=1111, device="cpu"))
     got, want = _run(data), _oracle(oracle, data)
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
 
 
-@pytest.mark.parametrize("m,k,l", [(128, 256, 1), (384, 2048 + 64, 3), (200, 1024, 2), (4096, 7168, 2)])
-def test_quantized_within_tolerance(oracle, m, k, l):
+@pytest.mark.parametrize("m,k,l", [(128, 256, 1), (384, 2048 + 64, 3), (200, 1024, 2), (4096, 7168, 2), (128, 64, 1),
+                                   (130, 192, 2), (1, 4096, 1)])
+def test_quantized_within_tolerance(oracle, path, m, k, l):
     """N(0,1) data: fp32 summation order differs from the oracle, so compare with the harness's
     rtol = atol = 1e-3 rule and the 1e-2 * max|ref| bound."""
     from eval_test_b200 import check, inputs
@@ -45,7 +56,7 @@ def test_quantized_within_tolerance(oracle, m, k, l):
     assert check.max_delta_ok(got, want)[0]
 
 
-def test_all_bit_patterns(oracle):
+def test_all_bit_patterns(oracle, path):
     """Every byte value (all 16 x 16 nibble pairs, negative zeros included) in A and in x."""
     from eval_test_b200 import inputs
     data = list(inputs.gemm_reference_style(256, 128, 1024, 2, seed=5, device="cpu"))
@@ -53,6 +64,24 @@ def test_all_bit_patterns(oracle):
     data = to_device(tuple(data))
     got, want = _run(data), _oracle(oracle, data)
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+def test_cluster_size_does_not_change_a_bit(monkeypatch):
+    """The tensor-core kernel splits K over the CTAs of a cluster; the partial sums are formed and added per fixed
+    K segment, so every cluster size must give the same bits (and so must a different M or L around the same rows)."""
+    from eval_test_b200 import inputs, nvfp4_gemv, shard
+    monkeypatch.delenv("NVFP4_GEMV_PATH", raising=False)
+    data = inputs.gemv_quantized(1024, 4096 + 192, 2, seed=21, device="cuda")
+    outs = []
+    for s in (1, 2, 4, 8):
+        monkeypatch.setenv("NVFP4_GEMV_SPLIT", str(s))
+        data[-1].zero_()
+        outs.append(_run(data).copy())
+    for o in outs[1:]:
+        assert np.array_equal(o.view(np.uint16), outs[0].view(np.uint16))
+    monkeypatch.delenv("NVFP4_GEMV_SPLIT")
+    part = _run(shard.shard_gemv(data, 1, 4))
+    assert np.array_equal(part.view(np.uint16), outs[0][256:512].view(np.uint16))
 
 
 def test_linearity_full_size():
