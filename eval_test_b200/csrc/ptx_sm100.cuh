@@ -280,6 +280,40 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
         }
     }
 }
+// Store one word into the shared memory of a CTA of the cluster (address from mapa_shared()).
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+// ------------------------------------------------------------------ cluster launch control (dynamic persistent scheduling)
+// Ask the hardware to cancel one cluster of this grid that has not started yet.  The 16-byte answer lands in this
+// CTA's shared memory at `result` (16-byte aligned) and completes 16 bytes on the mbarrier `bar`.
+// After an answer that says "nothing was cancelled" a CTA must not ask again.
+__device__ __forceinline__ void clc_try_cancel(uint32_t result, uint32_t bar) {
+    asm volatile("clusterlaunchcontrol.try_cancel.async.shared::cta.mbarrier::complete_tx::bytes.b128 [%0], [%1];" ::
+                     "r"(result), "r"(bar)
+                 : "memory");
+}
+// Decode an answer: returns true and the x index of the cancelled cluster's first CTA, or false.
+__device__ __forceinline__ bool clc_query(uint32_t result, uint32_t* first_ctaid_x) {
+    uint32_t ok, x;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p1;\n\t"
+        ".reg .b128 resp;\n\t"
+        "ld.shared.b128 resp, [%2];\n\t"
+        "clusterlaunchcontrol.query_cancel.is_canceled.pred.b128 p1, resp;\n\t"
+        "selp.u32 %0, 1, 0, p1;\n\t"
+        "mov.u32 %1, 0;\n\t"
+        "@p1 clusterlaunchcontrol.query_cancel.get_first_ctaid.v4.b32.b128 {%1, _, _, _}, resp;\n\t"
+        "}\n"
+        : "=r"(ok), "=r"(x)
+        : "r"(result)
+        : "memory");
+    *first_ctaid_x = x;
+    return ok != 0;
+}
+
 // Pair-wide TMEM allocation: the same warp of BOTH CTAs of the pair executes these.
 __device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_dst, uint32_t ncols) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
@@ -334,6 +368,10 @@ __device__ __forceinline__ void st_global_256_hint(void* p, const uint32_t (&v)[
 // 1024 bytes apart, descriptor version 1 (sm_100), layout type 2.
 __device__ __forceinline__ uint64_t make_desc_k_sw128(uint32_t saddr) {
     return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// The same with the 8-row groups `sbo` bytes apart (a multiple of 16).
+__device__ __forceinline__ uint64_t make_desc_k_sw128_sbo(uint32_t saddr, uint32_t sbo) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(sbo >> 4) << 32) | (1ull << 46) | (2ull << 61);
 }
 // Descriptor for one 512-byte scale-factor atom: 32 rows of 16 bytes, no swizzle, 8-row groups 128 bytes apart.
 __device__ __forceinline__ uint64_t make_desc_sf(uint32_t saddr) {

@@ -14,11 +14,9 @@ REFERENCE_TESTS = [(128, 256, 1), (128, 1536, 1), (128, 3072, 1), (256, 7168, 1)
 
 @pytest.fixture(params=["tensor", "alu"])
 def path(request, monkeypatch):
-    """Both GEMV kernels: the tensor-core stream (default) and the decode-on-CUDA-cores kernel."""
-    if request.param == "alu":
-        monkeypatch.setenv("NVFP4_GEMV_PATH", "alu")
-    else:
-        monkeypatch.delenv("NVFP4_GEMV_PATH", raising=False)
+    """Both GEMV kernels, each forced: the tensor-core stream and the decode-on-CUDA-cores kernel (the entry point
+    picks one by the number of 128-row tiles when nothing is forced)."""
+    monkeypatch.setenv("NVFP4_GEMV_PATH", request.param)
     return request.param
 
 
@@ -70,10 +68,10 @@ def test_cluster_size_does_not_change_a_bit(monkeypatch):
     """The tensor-core kernel splits K over the CTAs of a cluster; the partial sums are formed and added per fixed
     K segment, so every cluster size must give the same bits (and so must a different M or L around the same rows)."""
     from eval_test_b200 import inputs, nvfp4_gemv, shard
-    monkeypatch.delenv("NVFP4_GEMV_PATH", raising=False)
+    monkeypatch.setenv("NVFP4_GEMV_PATH", "tensor")
     data = inputs.gemv_quantized(1024, 4096 + 192, 2, seed=21, device="cuda")
     outs = []
-    for s in (1, 2, 4, 8):
+    for s in (1, 2):
         monkeypatch.setenv("NVFP4_GEMV_SPLIT", str(s))
         data[-1].zero_()
         outs.append(_run(data).copy())
@@ -81,7 +79,24 @@ def test_cluster_size_does_not_change_a_bit(monkeypatch):
         assert np.array_equal(o.view(np.uint16), outs[0].view(np.uint16))
     monkeypatch.delenv("NVFP4_GEMV_SPLIT")
     part = _run(shard.shard_gemv(data, 1, 4))
-    assert np.array_equal(part.view(np.uint16), outs[0][256:512].view(np.uint16))
+    assert np.array_equal(part.view(np.uint16), outs[0][:, 256:512].view(np.uint16))
+
+
+def test_default_dispatch_and_tensor_map_layouts(oracle, monkeypatch):
+    """Nothing forced: small problems go to the decode kernel, large ones to the tensor-core stream; the stream's
+    two ways of fetching A (one 5-D box per stage, one 128-row box per 256 elements) give the same bits; M that is
+    not a multiple of 8 and K beyond 65536 are served."""
+    from eval_test_b200 import inputs
+    monkeypatch.delenv("NVFP4_GEMV_PATH", raising=False)
+    for m, k, l in [(256, 1024, 1), (128 * 40, 1024, 1), (1000, 2048, 5), (1001, 1024 + 64, 5), (128, 65536 + 512, 1)]:
+        data = to_device(inputs.gemv_reference_style(m, k, l, seed=7, device="cpu"))
+        want = _oracle(oracle, data)
+        got = _run(data).copy()
+        assert np.array_equal(got.view(np.uint16), want.view(np.uint16)), (m, k, l)
+        monkeypatch.setenv("NVFP4_GEMV_ABOX", "3d")
+        data[-1].zero_()
+        assert np.array_equal(_run(data).view(np.uint16), want.view(np.uint16)), (m, k, l, "3d")
+        monkeypatch.delenv("NVFP4_GEMV_ABOX")
 
 
 def test_linearity_full_size():
