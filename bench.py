@@ -57,8 +57,8 @@ class GemvWorkload:
     name = "gemv_m16384_k16384_l4"
     metric = "nvfp4_gemv_hbm_gbs"
     unit, per = "GB/s", 1e9
-    dtype = "e2m1 x ue4m3 scales, int32 block dot, fp32 accumulate, fp16 out"
-    bound, kernel, scaling = "hbm", "gemv_kernel", "weak"
+    dtype = "e2m1 x ue4m3 scales, block-scaled tensor-core products, fp32 accumulate, fp16 out"
+    bound, kernel, scaling = "hbm", "gemv_tc_kernel", "weak"
 
     def __init__(self, m=16384, k=16384, l=4):
         self.m, self.k, self.l = m, k, l
