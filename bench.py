@@ -356,7 +356,7 @@ class QuantizeWorkload:
 
     def run(self, data):
         from eval_test_b200 import quantize
-        data[1] = quantize.quantize_operand(data[0])
+        data[1] = quantize.quantize_operand(data[0], ref_scales=False)   # one launch: the kernel alone
         return data[1]
 
     def io(self, data):

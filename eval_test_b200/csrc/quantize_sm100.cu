@@ -23,69 +23,84 @@ __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
     return r;
 }
 
-// A warp takes 32 consecutive blocks (512 floats = 2 KB) of the flattened [L*rows][K] operand per step: load i of a
-// lane is float4 number i*32 + lane of that span, so every load instruction is one contiguous 512-byte access.
-// Four neighbouring lanes hold the four quarters of one block: the block maximum comes from two shuffles, each lane
-// quantises its 4 values to 2 bytes and stores them (64 contiguous bytes per warp and store instruction); the lane
-// holding the first quarter also writes the scale byte.
+// A warp takes 32 consecutive blocks (512 floats = 2 KB) of the flattened [L*rows][K] operand per step and every
+// lane one whole block: four 16-byte loads (the four instructions of a warp together read the 2 KB once; L1 serves
+// the second half of each sector), block maximum, scale, 16 products, 8 conversions - all in the lane, no shuffles -
+// then one 8-byte store of the packed block (256 contiguous bytes per warp).  Four neighbouring lanes hold the four
+// k-blocks of one row that share a 4-byte group of a swizzle atom: their scale bytes are gathered into one 32-bit
+// store when K % 64 == 0.  The loads of the warp's next span are issued before the current one is processed.
 __global__ void __launch_bounds__(256)
 quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_sw, int rows,
                     int K, int L, long long total_blocks) {
-    const int kbs = K / 16;
-    const int R = (rows + 127) / 128, Kb4 = (kbs + 3) / 4;
+    const unsigned kbs = (unsigned)(K / 16);
+    const int R = (rows + 127) / 128, Kb4 = (int)(kbs + 3) / 4;
     const int lane = threadIdx.x & 31;
     const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
     const long long spans = (total_blocks + 31) / 32;
-    const bool rows_of_8 = (kbs & 7) == 0;   // then the 8 blocks of one load step lie in one row
+    const bool words = (kbs & 3) == 0;       // then lanes 4a..4a+3 hold one aligned word of one atom
+    const bool uniform_row = (kbs & 31) == 0;   // then a span lies in one row
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+
+    auto load_span = [&](long long sp, float4 (&v)[4]) {
+        const long long blk = sp * 32 + lane;
+        const float4* src = reinterpret_cast<const float4*>(x) + blk * 4;
+        const bool live = blk < total_blocks;
+#pragma unroll
+        for (int i = 0; i < 4; i++) v[i] = live ? __ldg(src + i) : zero4;
+    };
+
+    float4 v[4], nxt[4];
+    if (warp0 < spans) load_span(warp0, v);
     for (long long sp = warp0; sp < spans; sp += nwarps) {
-        const float4* src = reinterpret_cast<const float4*>(x) + sp * 128;
-        float4 v[4];
-        bool live[4];
+        const bool more = sp + nwarps < spans;
+        if (more) load_span(sp + nwarps, nxt);
+        const unsigned blk = (unsigned)(sp * 32) + (unsigned)lane;      // total_blocks < 2^31 (checked by the caller)
+        const bool live = (long long)blk < total_blocks;
+        float amax = 0.f;
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            const long long blk = sp * 32 + i * 8 + (lane >> 2);
-            live[i] = blk < total_blocks;
-            v[i] = live[i] ? __ldg(src + i * 32 + lane) : make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int i = 0; i < 4; i++)
+            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+        const float want = fminf(__fmul_rn(amax, (float)(1.0 / 6.0)), 448.0f);
+        const __nv_fp8_storage_t sbits = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
+        const __half_raw hr = __nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3);
+        const float s = __half2float(*reinterpret_cast<const __half*>(&hr));
+        uint32_t w0 = 0, w1 = 0;
+        if (s > 0.f) {
+            const float rs = __frcp_rn(s);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const uint32_t h = cvt_e2m1x2(__fmul_rn(v[i].x, rs), __fmul_rn(v[i].y, rs)) |
+                                   (cvt_e2m1x2(__fmul_rn(v[i].z, rs), __fmul_rn(v[i].w, rs)) << 8);
+                if (i < 2) w0 |= h << (16 * i);
+                else w1 |= h << (16 * (i - 2));
+            }
         }
-        // row and k-block of the span's first block: one warp-uniform division per span
-        const unsigned b0 = (unsigned)(sp * 32);
-        unsigned lr_s = b0 / (unsigned)kbs, kb_s = b0 - lr_s * (unsigned)kbs;
+        if (live) *reinterpret_cast<uint2*>(packed + (size_t)blk * 8) = make_uint2(w0, w1);
+        // where this block's scale byte goes
+        unsigned lr, kb;
+        if (uniform_row) {
+            const unsigned b0 = (unsigned)(sp * 32);
+            lr = b0 / kbs; kb = b0 - lr * kbs + (unsigned)lane;
+        } else {
+            lr = blk / kbs; kb = blk - lr * kbs;
+        }
+        const unsigned l = lr / (unsigned)rows, r = lr - l * (unsigned)rows;
+        const size_t off = ((size_t)l * R + r / 128) * (size_t)Kb4 * 512 + (size_t)(kb / 4) * 512 + (r % 32) * 16 +
+                           ((r % 128) / 32) * 4 + (kb % 4);
+        if (words) {
+            // (the operand ends on a multiple of 4 blocks here, so the 4 lanes of a group are live together)
+            uint32_t word = (uint32_t)sbits;
+            word |= __shfl_down_sync(0xffffffffu, (uint32_t)sbits, 1) << 8;
+            word |= __shfl_down_sync(0xffffffffu, (uint32_t)sbits, 2) << 16;
+            word |= __shfl_down_sync(0xffffffffu, (uint32_t)sbits, 3) << 24;
+            if (live && (lane & 3) == 0) *reinterpret_cast<uint32_t*>(sf_sw + off) = word;
+        } else if (live) {
+            sf_sw[off] = (uint8_t)sbits;
+        }
+        if (more) {
 #pragma unroll
-        for (int i = 0; i < 4; i++) {
-            float amax = fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w)));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-            amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
-            const float want = fminf(__fmul_rn(amax, (float)(1.0 / 6.0)), 448.0f);
-            const __nv_fp8_storage_t sbits = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
-            const __half_raw hr = __nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3);
-            const float s = __half2float(*reinterpret_cast<const __half*>(&hr));
-            uint32_t w = 0;
-            if (s > 0.f) {
-                const float rs = __frcp_rn(s);
-                w = cvt_e2m1x2(__fmul_rn(v[i].x, rs), __fmul_rn(v[i].y, rs)) |
-                    (cvt_e2m1x2(__fmul_rn(v[i].z, rs), __fmul_rn(v[i].w, rs)) << 8);
-            }
-            // position of this lane's block
-            unsigned lr, kb;
-            if (rows_of_8) {
-                lr = lr_s; kb = kb_s + (unsigned)(lane >> 2);         // kb_s is a multiple of 8, so no wrap inside
-                kb_s += 8;
-                if (kb_s >= (unsigned)kbs) { kb_s -= (unsigned)kbs; lr_s++; }
-            } else {
-                const unsigned blk = b0 + (unsigned)(i * 8 + (lane >> 2));
-                lr = blk / (unsigned)kbs; kb = blk - lr * (unsigned)kbs;
-            }
-            if (live[i]) {
-                // packed bytes of the whole operand: 8 per block, this lane holds quarter lane % 4
-                *reinterpret_cast<uint16_t*>(packed + ((size_t)b0 + i * 8 + (lane >> 2)) * 8 + (lane & 3) * 2) = (uint16_t)w;
-                if ((lane & 3) == 0) {
-                    const unsigned l = lr / (unsigned)rows, r = lr - l * (unsigned)rows;
-                    const size_t off = ((size_t)l * R + r / 128) * (size_t)Kb4 * 512 + (size_t)(kb / 4) * 512 +
-                                       (r % 32) * 16 + ((r % 128) / 32) * 4 + (kb % 4);
-                    sf_sw[off] = (uint8_t)sbits;
-                }
-            }
+            for (int i = 0; i < 4; i++) v[i] = nxt[i];
         }
     }
 }
@@ -98,7 +113,7 @@ extern "C" int nvfp4_quantize_f32(const void* x, void* packed, void* sf_sw, int 
     if (!x || !packed || !sf_sw) return NVFP4_ERR_NULL;
     if (rows <= 0 || K <= 0 || L <= 0) return NVFP4_ERR_SHAPE;
     if (K % 16 != 0) return NVFP4_ERR_K_MULTIPLE;
-    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 7)) return NVFP4_ERR_ALIGN;
+    if (((uintptr_t)x & 15) || ((uintptr_t)packed & 7) || ((uintptr_t)sf_sw & 3)) return NVFP4_ERR_ALIGN;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -111,8 +126,15 @@ extern "C" int nvfp4_quantize_f32(const void* x, void* packed, void* sf_sw, int 
     }
     const long long total = (long long)L * rows * (K / 16);
     if (total >= (1ll << 31)) return NVFP4_ERR_UNSUPPORTED;   // block indices are 32-bit inside the kernel
-    long long blocks = (total + 255) / 256;
-    const long long cap = (long long)sm_count(dev) * 16;
+    // a grid-stride loop over spans: as many blocks as are resident at once (no partial last wave)
+    static int per_sm[64] = {};
+    if (dev < 64 && !per_sm[dev]) {
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_f32_kernel, 256, 0) != cudaSuccess || n < 1) n = 4;
+        per_sm[dev] = n;
+    }
+    long long blocks = (total + 255) / 256;   // 8 warps x 32 blocks per thread block and step
+    const long long cap = (long long)sm_count(dev) * (dev < 64 ? per_sm[dev] : 4);
     if (blocks > cap) blocks = cap;
     quantize_f32_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float*)x, (uint8_t*)packed, (uint8_t*)sf_sw, rows, K, L,
                                                           total);

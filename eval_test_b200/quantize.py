@@ -10,9 +10,12 @@ import torch
 from . import _lib, formats as F
 
 
-def quantize_operand(x: torch.Tensor):
+def quantize_operand(x: torch.Tensor, ref_scales: bool = True):
     """x: CUDA fp32 ``[L, rows, K]`` (contiguous) -> (operand ``[rows, K/2, L]`` float4_e2m1fn_x2,
-    row-major scales ``[rows, K/16, L]`` float8_e4m3fn, 6-D swizzled view)."""
+    row-major scales ``[rows, K/16, L]`` float8_e4m3fn, 6-D swizzled view).
+
+    The row-major scales are what the reference's tuples carry for its own checker; the kernels read only the
+    swizzled buffer.  ``ref_scales=False`` skips the torch gather that rebuilds them (the second entry is None)."""
     if not (x.is_cuda and x.dtype == torch.float32 and x.dim() == 3 and x.is_contiguous()):
         raise ValueError("quantize_operand: expected a contiguous CUDA float32 tensor [L, rows, K]")
     L, rows, K = x.shape
@@ -22,6 +25,5 @@ def quantize_operand(x: torch.Tensor):
         code = _lib.load().nvfp4_quantize_f32(x.data_ptr(), packed.data_ptr(), buf.data_ptr(), rows, K, L,
                                               torch.cuda.current_stream(x.device).cuda_stream)
     _lib.check(code, "nvfp4_quantize_f32")
-    sf = F.unswizzle_scales(buf, rows, K, L)
-    return (F.batch_last(packed).view(torch.float4_e2m1fn_x2), F.batch_last(sf).view(torch.float8_e4m3fn),
-            F.permuted_view(buf, rows, K, L))
+    sf = F.batch_last(F.unswizzle_scales(buf, rows, K, L)).view(torch.float8_e4m3fn) if ref_scales else None
+    return (F.batch_last(packed).view(torch.float4_e2m1fn_x2), sf, F.permuted_view(buf, rows, K, L))
