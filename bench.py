@@ -239,6 +239,27 @@ class DualGemmWorkload(GemmWorkload):
         from oracle import nvfp4_oracle as O
         return O.c_dual_gemm(*args)
 
+class DualGemmNvfp4Workload(DualGemmWorkload):
+    """The same up-projection with the result emitted as NVFP4 (packed e2m1 + swizzled block scales) for the
+    down-projection: the quantiser fused into the epilogue.  Same flops; 33 MB written per step instead of 117 MB."""
+    name = "dual_gemm_nvfp4out_m4096_n14336_k4096"
+    metric = "nvfp4_dual_gemm_nvfp4out_tflops"
+    dtype = "e2m1 x ue4m3 scales on tcgen05 (kind::mxf4nvf4), fp32 accumulate, fp16 rounding, NVFP4 out"
+
+    def small(self):
+        return DualGemmNvfp4Workload(m=2048, n=7168, k=4096)
+
+    def run(self, data):
+        from eval_test_b200 import nvfp4_dual_gemm
+        self.last = nvfp4_dual_gemm.custom_kernel_nvfp4(data)
+        return self.last
+
+    def io(self, data):
+        a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, _ = data
+        op, _, sf_p = getattr(self, "last", None) or self.run(data)
+        return [a, b1, b2, sfa_p, sfb1_p, sfb2_p], [op, sf_p]
+
+
 class GroupedGemmWorkload:
     """MoE expert layer: 64 groups, N = 4096, K = 7168, M_g ~ Poisson(128) clipped to [0, 1024] from
     numpy.random.default_rng(0).  At this M the layer is HBM-bound (every weight byte is read once), so the
@@ -385,6 +406,7 @@ class QuantizeWorkload:
 
 
 WORKLOADS = {"gemv": GemvWorkload, "gemm": GemmWorkload, "dual_gemm": DualGemmWorkload,
+             "dual_gemm_nvfp4": DualGemmNvfp4Workload,
              "grouped_gemm": GroupedGemmWorkload, "quantize": QuantizeWorkload}
 
 

@@ -8,6 +8,7 @@
 
 #include "nvfp4_internal.h"
 #include "ptx_sm100.cuh"
+#include "quant_block.cuh"
 
 namespace nvfp4 {
 
@@ -32,6 +33,8 @@ struct GemmParams {
     const uint8_t* sfb;   // swizzled scales of B (B1 for the dual GEMM)
     const uint8_t* sfb2;  // swizzled scales of B2 (dual GEMM only)
     __half* c;            // [L][M][N]
+    uint8_t* cq = nullptr;   // NVFP4 output instead of fp16: packed e2m1 [L][M][N/2] ...
+    uint8_t* sfc = nullptr;  // ... and its block scales, swizzled [L][ceil(M/128)][N/64][512]
     int M, N, K, L;
     float alpha;
     int* status;
@@ -159,14 +162,48 @@ __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32]
     }
 }
 
+// NVFP4 output: where one thread (one row) puts the packed codes and scale bytes of the tile, and the first
+// chunk of a pair of 32-column chunks, held until the second one completes a 32-byte sector and a 4-byte scale group.
+struct QuantOut {
+    uint8_t* codes;    // the row's packed bytes at the tile's first column
+    uint8_t* scales;   // the row's 4-byte group in the scale atom of the tile's first 64 columns
+    uint32_t held[5];
+};
+
+// 32 results of one row -> fp16 (the rounding of the fp16 output) -> two blocks of NVFP4, exactly what
+// nvfp4_quantize_f32 makes of the fp16 output.  Chunk cc of the tile; odd chunks store their pair.
+template <bool DUAL>
+__device__ __forceinline__ void store_chunk_q(QuantOut& q, int cc, const uint32_t (&v)[32], const uint32_t (&w)[32],
+                                              float alpha, bool pred) {
+    float f[32];
+#pragma unroll
+    for (int i = 0; i < 32; i++) {
+        const float x = alpha * __uint_as_float(v[i]);
+        const float r = DUAL ? silu_mul(x, alpha * __uint_as_float(w[i])) : x;
+        f[i] = __half2float(__float2half_rn(r));
+    }
+    uint32_t a0, a1, b0, b1;
+    const uint32_t s0 = quantize_block16(f, a0, a1);
+    const uint32_t s1 = quantize_block16(f + 16, b0, b1);
+    if ((cc & 1) == 0) {
+        q.held[0] = a0; q.held[1] = a1; q.held[2] = b0; q.held[3] = b1;
+        q.held[4] = s0 | (s1 << 8);
+    } else if (pred) {
+        const uint32_t o[8] = {q.held[0], q.held[1], q.held[2], q.held[3], a0, a1, b0, b1};
+        st_global_256(q.codes + (cc - 1) * 16, o);
+        *reinterpret_cast<uint32_t*>(q.scales + (cc >> 1) * 512) = q.held[4] | (s0 << 16) | (s1 << 24);
+    }
+}
+
 // Epilogue of one tile for one warp (its 32 accumulator rows).  C0 is the first 32-column chunk, relative to
 // the accumulator base, that this buffer shares with the other one (OVC chunks; OVC = 0: nothing shared).
 // The shared chunks are pulled into registers first and released at once, so the next tile's MMAs wait only
 // for those loads, not for the conversion and stores.
 // CLUSTER: ovl_free is a shared::cluster address (the barrier may live in the peer CTA).
-template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false>
+// QOUT: NVFP4 output through q instead of fp16 through crow.
+template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, bool row_ok, int n0, int N, float alpha,
-                                              uint32_t ovl_free, int lane) {
+                                              uint32_t ovl_free, int lane, QuantOut* q = nullptr) {
     constexpr int NCH = BN / 32;
     uint32_t ov[OVC > 0 ? OVC : 1][32];
     if (OVC > 0) {
@@ -191,7 +228,11 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, boo
         if (!v_pre || (DUAL && !w_pre)) tc_wait_ld();
         const bool pred = row_ok && n0 + cc * 32 < N;
         // (index clamps only keep the never-taken branch in range for the compiler)
-        store_chunk<DUAL>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+        if (QOUT)
+            store_chunk_q<DUAL>(*q, cc, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+                                w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
+                                pred);
+        else store_chunk<DUAL>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
                           w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
                           pred);
     }

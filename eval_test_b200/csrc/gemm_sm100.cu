@@ -37,7 +37,8 @@
 namespace nvfp4 {
 
 // BN: output columns per tile (GEMM: 128 or 256; DUAL: 128, the MMA is 256 wide over [B1;B2]).
-template <int BN, bool DUAL, bool GROUPED, int STAGES>
+// QOUT: the epilogue writes NVFP4 (packed codes + swizzled block scales) instead of fp16.
+template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
@@ -224,13 +225,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
             tc_fence_after_sync();
             const uint32_t t_lane = tmem_base + buf * ACC1_OFF + ((uint32_t)(q * 32) << 16);
-            __half* crow = ti.c + (size_t)(row < ti.M ? row : 0) * ti.N + n0;
+            const int srow = row < ti.M ? row : 0;
+            __half* crow = ti.c + (size_t)srow * ti.N + n0;
+            QuantOut qo;
+            if (QOUT) {
+                const size_t grow = (size_t)ti.l * ti.M + srow;                       // row of the [L*M][N] output
+                qo.codes = p.cq + grow * (size_t)(ti.N / 2) + n0 / 2;
+                const size_t rb = (size_t)ti.l * ((ti.M + 127) / 128) + srow / 128;   // 128-row block of the scales
+                qo.scales = p.sfc + (rb * (size_t)(ti.N / 64) + n0 / 64) * 512 + (srow % 32) * 16 + ((srow % 128) / 32) * 4;
+            }
             // buffer 0 shares its last OVERLAP columns, buffer 1 its first
             if (buf == 0)
-                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha,
-                                                                      ovl_free, lane);
+                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS, false, QOUT>(t_lane, crow, row < ti.M, n0, ti.N,
+                                                                                   p.alpha, ovl_free, lane, &qo);
             else
-                epilogue_tile<BN, DUAL, 0, OV_CHUNKS>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free, lane);
+                epilogue_tile<BN, DUAL, 0, OV_CHUNKS, false, QOUT>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free,
+                                                                  lane, &qo);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
@@ -277,14 +287,14 @@ int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L
     return NVFP4_OK;
 }
 
-template <int BN, bool DUAL, bool GROUPED, int STAGES>
+template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                        cudaStream_t stream) {
     constexpr int MMA_N = DUAL ? 2 * BN : BN;
     constexpr size_t STAGE = 128 * 128 + MMA_N * 128 + 2048 + (MMA_N / 128) * 2048;
     constexpr size_t SMEM = STAGES * STAGE + 1024;  // + slack for the 1024-byte alignment
     static_assert(SMEM <= 227 * 1024 - 256, "shared memory");
-    auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES>;
+    auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES, QOUT>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -388,6 +398,33 @@ extern "C" int nvfp4_dual_gemm(const void* a, const void* b1, const void* b2, co
     if (pair_mode != 0 && M >= 256 && (pair_mode == 1 || pair_kernel_suits(M, N, K, L, true, dev)))
         return launch_gemm_pair(true, ta, tb1, tb2, p, (cudaStream_t)stream);
     return launch_gemm<128, true, false, 4>(ta, tb1, tb2, p, (cudaStream_t)stream);
+}
+
+extern "C" int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const void* sfa_sw,
+                                     const void* sfb1_sw, const void* sfb2_sw, void* c_packed, void* sfc_sw, int M, int N,
+                                     int K, int L, float alpha, void* stream) {
+    const void* ptrs[8] = {a, b1, b2, sfa_sw, sfb1_sw, sfb2_sw, sfc_sw, c_packed};
+    int rc = check_common(ptrs, 8, M, N, K, L);
+    if (rc) return rc;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    CUtensorMap ta, tb1, tb2;
+    rc = make_operand_tmap(&ta, a, M, K, L, 128);
+    if (rc) return rc;
+    rc = make_operand_tmap(&tb1, b1, N, K, L, 128);
+    if (rc) return rc;
+    rc = make_operand_tmap(&tb2, b2, N, K, L, 128);
+    if (rc) return rc;
+    GemmParams p;
+    p.sfa = (const uint8_t*)sfa_sw; p.sfb = (const uint8_t*)sfb1_sw; p.sfb2 = (const uint8_t*)sfb2_sw;
+    p.c = nullptr; p.cq = (uint8_t*)c_packed; p.sfc = (uint8_t*)sfc_sw;
+    p.M = M; p.N = N; p.K = K; p.L = L; p.alpha = alpha;
+    p.status = status_word(dev);
+    p.budget_ns = wait_budget_ns();
+    p.table = nullptr; p.G = 0;
+    p.total_tiles = ((M + BM - 1) / BM) * (N / 128) * L;
+    return launch_gemm<128, true, false, 4, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------------ grouped GEMM

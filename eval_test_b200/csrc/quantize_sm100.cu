@@ -13,15 +13,9 @@
 #include <stdint.h>
 
 #include "nvfp4_internal.h"
+#include "quant_block.cuh"
 
 namespace nvfp4 {
-
-// Two floats -> one byte of two e2m1 codes (first value in the low nibble), round to nearest even, saturating.
-__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
-    uint16_t r;
-    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u16.u8 %0, t; }" : "=h"(r) : "f"(hi), "f"(lo));
-    return r;
-}
 
 // A warp takes 32 consecutive blocks (512 floats = 2 KB) of the flattened [L*rows][K] operand per step and every
 // lane one whole block: four 16-byte loads (the four instructions of a warp together read the 2 KB once; L1 serves
@@ -57,25 +51,10 @@ quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, u
         if (more) load_span(sp + nwarps, nxt);
         const unsigned blk = (unsigned)(sp * 32) + (unsigned)lane;      // total_blocks < 2^31 (checked by the caller)
         const bool live = (long long)blk < total_blocks;
-        float amax = 0.f;
-#pragma unroll
-        for (int i = 0; i < 4; i++)
-            amax = fmaxf(amax, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
-        const float want = fminf(__fmul_rn(amax, (float)(1.0 / 6.0)), 448.0f);
-        const __nv_fp8_storage_t sbits = __nv_cvt_float_to_fp8(want, __NV_SATFINITE, __NV_E4M3);
-        const __half_raw hr = __nv_cvt_fp8_to_halfraw(sbits, __NV_E4M3);
-        const float s = __half2float(*reinterpret_cast<const __half*>(&hr));
-        uint32_t w0 = 0, w1 = 0;
-        if (s > 0.f) {
-            const float rs = __frcp_rn(s);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                const uint32_t h = cvt_e2m1x2(__fmul_rn(v[i].x, rs), __fmul_rn(v[i].y, rs)) |
-                                   (cvt_e2m1x2(__fmul_rn(v[i].z, rs), __fmul_rn(v[i].w, rs)) << 8);
-                if (i < 2) w0 |= h << (16 * i);
-                else w1 |= h << (16 * (i - 2));
-            }
-        }
+        const float xs[16] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w,
+                              v[2].x, v[2].y, v[2].z, v[2].w, v[3].x, v[3].y, v[3].z, v[3].w};
+        uint32_t w0, w1;
+        const uint32_t sbits = quantize_block16(xs, w0, w1);
         if (live) *reinterpret_cast<uint2*>(packed + (size_t)blk * 8) = make_uint2(w0, w1);
         // where this block's scale byte goes
         unsigned lr, kb;
@@ -90,10 +69,10 @@ quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, u
                            ((r % 128) / 32) * 4 + (kb % 4);
         if (words) {
             // (the operand ends on a multiple of 4 blocks here, so the 4 lanes of a group are live together)
-            uint32_t word = (uint32_t)sbits;
-            word |= __shfl_down_sync(0xffffffffu, (uint32_t)sbits, 1) << 8;
-            word |= __shfl_down_sync(0xffffffffu, (uint32_t)sbits, 2) << 16;
-            word |= __shfl_down_sync(0xffffffffu, (uint32_t)sbits, 3) << 24;
+            uint32_t word = sbits;
+            word |= __shfl_down_sync(0xffffffffu, sbits, 1) << 8;
+            word |= __shfl_down_sync(0xffffffffu, sbits, 2) << 16;
+            word |= __shfl_down_sync(0xffffffffu, sbits, 3) << 24;
             if (live && (lane & 3) == 0) *reinterpret_cast<uint32_t*>(sf_sw + off) = word;
         } else if (live) {
             sf_sw[off] = (uint8_t)sbits;

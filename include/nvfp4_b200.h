@@ -63,6 +63,16 @@ int nvfp4_dual_gemm(const void* a, const void* b1, const void* b2, const void* s
                     const void* sfb1_sw, const void* sfb2_sw, void* c,
                     int M, int N, int K, int L, float alpha, void* stream);
 
+/* The same dual GEMM with the result emitted as NVFP4, ready to be the A operand of the next GEMM (the
+ * down-projection of an MLP): c_packed [L][M][N/2] e2m1 codes and sfc_sw, their block-16 e4m3 scales in the
+ * swizzled layout [L][ceil(M/128)][N/64][512] (rows padded to 128; padding rows are not written).
+ * Bit for bit nvfp4_quantize_f32 applied to the fp16 output of nvfp4_dual_gemm.
+ * No counterpart in the reference, whose dual GEMM ends in fp16 (eval/nvfp4_dual_gemm/reference.py:11-45).
+ * c_packed 32-byte aligned, the rest 16-byte aligned; N % 128 == 0, K % 256 == 0. */
+int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const void* sfa_sw,
+                          const void* sfb1_sw, const void* sfb2_sw, void* c_packed, void* sfc_sw,
+                          int M, int N, int K, int L, float alpha, void* stream);
+
 /* One problem of a grouped GEMM (L = 1): c[M][N] = fp16(alpha * (a*sfa) @ (b*sfb)^T). */
 typedef struct nvfp4_group {
     const void* a;       /* [M][K/2] */
