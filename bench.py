@@ -354,6 +354,7 @@ class QuantizeWorkload:
     metric = "nvfp4_quantize_hbm_gbs"
     unit, per = "GB/s", 1e9
     dtype = "fp32 in, e2m1 + e4m3 block scales out"
+    cpu_dtype = dtype
     bound, kernel, scaling = "hbm", "quantize_f32_kernel", "weak"
 
     def __init__(self, rows=16384, k=16384):
@@ -502,7 +503,9 @@ def run_reference(args, wl):
     val = units / dt / wl.per
     line = {"impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": args.gpus,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
-            "scaling": wl.scaling, "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
+            "scaling": wl.scaling, "vs_baseline": None,
+            "dtype": getattr(wl, "cpu_dtype", "e2m1 x ue4m3 scales, exact int32 block dots, fp32 accumulate, fp16 out (CPU)"),
+            "data": "synthetic",
             "config": wl.config(args.gpus),
             "cpu_baseline": {"value": val, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
                              "sample": "each step = " + what},
