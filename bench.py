@@ -574,19 +574,19 @@ def main():
     barrier()
 
     # ---- timed region: K steps, device-resident inputs ----
-    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+    # One kernel launch per step and nothing else on the stream, so the average launch duration is the event time
+    # over the region divided by the launches (launch gaps included: an upper bound of the kernel's own time; an
+    # event pair around every launch would put two more stream operations between the kernels).
     t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
         t_begin.record(stream)
-        for s, e in ev:
-            s.record(stream)
+        for _ in range(args.steps):
             wl.run(data)
-            e.record(stream)
         t_end.record(stream)
         barrier()
     total_ms = t_begin.elapsed_time(t_end)
-    kern_ms = sum(s.elapsed_time(e) for s, e in ev) / args.steps
+    kern_ms = total_ms / args.steps
     status = _lib.device_status(local_rank)
     assert status == 0, f"device status {status}: {_lib.strerror(status)}"
 

@@ -23,8 +23,11 @@ namespace nvfp4 {
 // then one 8-byte store of the packed block (256 contiguous bytes per warp).  Four neighbouring lanes hold the four
 // k-blocks of one row that share a 4-byte group of a swizzle atom: their scale bytes are gathered into one 32-bit
 // store when K % 64 == 0.  The loads of the warp's next span are issued before the current one is processed.
+// KIND: 0 fp32, 1 fp16, 2 bf16 input (16-bit inputs: two 16-byte loads per lane; values are widened to fp32, which is
+// exact, and quantised by the same rule).
+template <int KIND>
 __global__ void __launch_bounds__(256)
-quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_sw, int rows,
+quantize_kernel(const void* __restrict__ x, uint8_t* __restrict__ packed, uint8_t* __restrict__ sf_sw, int rows,
                     int K, int L, long long total_blocks) {
     const unsigned kbs = (unsigned)(K / 16);
     const int R = (rows + 127) / 128, Kb4 = (int)(kbs + 3) / 4;
@@ -34,25 +37,41 @@ quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, u
     const long long spans = (total_blocks + 31) / 32;
     const bool words = (kbs & 3) == 0;       // then lanes 4a..4a+3 hold one aligned word of one atom
     const bool uniform_row = (kbs & 31) == 0;   // then a span lies in one row
-    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    constexpr int NV = KIND == 0 ? 4 : 2;    // 16-byte loads per block
+    const uint4 zero4 = make_uint4(0u, 0u, 0u, 0u);
 
-    auto load_span = [&](long long sp, float4 (&v)[4]) {
+    auto load_span = [&](long long sp, uint4 (&v)[NV]) {
         const long long blk = sp * 32 + lane;
-        const float4* src = reinterpret_cast<const float4*>(x) + blk * 4;
+        const uint4* src = reinterpret_cast<const uint4*>(x) + blk * NV;
         const bool live = blk < total_blocks;
 #pragma unroll
-        for (int i = 0; i < 4; i++) v[i] = live ? __ldg(src + i) : zero4;
+        for (int i = 0; i < NV; i++) v[i] = live ? __ldg(src + i) : zero4;
     };
 
-    float4 v[4], nxt[4];
+    uint4 v[NV], nxt[NV];
     if (warp0 < spans) load_span(warp0, v);
     for (long long sp = warp0; sp < spans; sp += nwarps) {
         const bool more = sp + nwarps < spans;
         if (more) load_span(sp + nwarps, nxt);
         const unsigned blk = (unsigned)(sp * 32) + (unsigned)lane;      // total_blocks < 2^31 (checked by the caller)
         const bool live = (long long)blk < total_blocks;
-        const float xs[16] = {v[0].x, v[0].y, v[0].z, v[0].w, v[1].x, v[1].y, v[1].z, v[1].w,
-                              v[2].x, v[2].y, v[2].z, v[2].w, v[3].x, v[3].y, v[3].z, v[3].w};
+        float xs[16];
+#pragma unroll
+        for (int i = 0; i < NV; i++) {
+            const uint32_t wv[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                if (KIND == 0) {
+                    xs[4 * i + j] = __uint_as_float(wv[j]);
+                } else if (KIND == 1) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&wv[j]));
+                    xs[8 * i + 2 * j] = f.x; xs[8 * i + 2 * j + 1] = f.y;
+                } else {   // bf16 is the upper half of an fp32
+                    xs[8 * i + 2 * j] = __uint_as_float(wv[j] << 16);
+                    xs[8 * i + 2 * j + 1] = __uint_as_float(wv[j] & 0xffff0000u);
+                }
+            }
+        }
         uint32_t w0, w1;
         const uint32_t sbits = quantize_block16(xs, w0, w1);
         if (live) *reinterpret_cast<uint2*>(packed + (size_t)blk * 8) = make_uint2(w0, w1);
@@ -79,7 +98,7 @@ quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, u
         }
         if (more) {
 #pragma unroll
-            for (int i = 0; i < 4; i++) v[i] = nxt[i];
+            for (int i = 0; i < NV; i++) v[i] = nxt[i];
         }
     }
 }
@@ -88,7 +107,8 @@ quantize_f32_kernel(const float* __restrict__ x, uint8_t* __restrict__ packed, u
 
 using namespace nvfp4;
 
-extern "C" int nvfp4_quantize_f32(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream) {
+template <int KIND>
+static int quantize_any(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream) {
     if (!x || !packed || !sf_sw) return NVFP4_ERR_NULL;
     if (rows <= 0 || K <= 0 || L <= 0) return NVFP4_ERR_SHAPE;
     if (K % 16 != 0) return NVFP4_ERR_K_MULTIPLE;
@@ -109,14 +129,23 @@ extern "C" int nvfp4_quantize_f32(const void* x, void* packed, void* sf_sw, int 
     static int per_sm[64] = {};
     if (dev < 64 && !per_sm[dev]) {
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_f32_kernel, 256, 0) != cudaSuccess || n < 1) n = 4;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, quantize_kernel<KIND>, 256, 0) != cudaSuccess || n < 1) n = 4;
         per_sm[dev] = n;
     }
     long long blocks = (total + 255) / 256;   // 8 warps x 32 blocks per thread block and step
     const long long cap = (long long)sm_count(dev) * (dev < 64 ? per_sm[dev] : 4);
     if (blocks > cap) blocks = cap;
-    quantize_f32_kernel<<<(unsigned)blocks, 256, 0, st>>>((const float*)x, (uint8_t*)packed, (uint8_t*)sf_sw, rows, K, L,
-                                                          total);
+    quantize_kernel<KIND><<<(unsigned)blocks, 256, 0, st>>>(x, (uint8_t*)packed, (uint8_t*)sf_sw, rows, K, L, total);
     e = cudaGetLastError();
     return e == cudaSuccess ? NVFP4_OK : (int)e;
+}
+
+extern "C" int nvfp4_quantize_f32(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream) {
+    return quantize_any<0>(x, packed, sf_sw, rows, K, L, stream);
+}
+extern "C" int nvfp4_quantize_f16(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream) {
+    return quantize_any<1>(x, packed, sf_sw, rows, K, L, stream);
+}
+extern "C" int nvfp4_quantize_bf16(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream) {
+    return quantize_any<2>(x, packed, sf_sw, rows, K, L, stream);
 }

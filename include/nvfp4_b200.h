@@ -108,8 +108,11 @@ int nvfp4_grouped_gemm_noalloc(const nvfp4_group_t* groups, int G, float alpha, 
 /* fp32 -> NVFP4 quantiser (the step in front of the path; the reference has no counterpart, its generators draw
  * bit patterns, eval/nvfp4_gemm/reference.py:35-38): x is [L][rows][K] fp32 row-major; writes packed e2m1
  * [L][rows][K/2] and the e4m3 block scales (amax/6, RNE) directly in the swizzled layout (rows padded to 128,
- * padding zeroed).  K % 16 == 0; x 16-byte, packed 8-byte aligned. */
+ * padding zeroed).  K % 16 == 0; x 16-byte, packed 8-byte, sf_sw 4-byte aligned. */
 int nvfp4_quantize_f32(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream);
+/* The same for fp16 and bf16 activations (widened to fp32 exactly, then the same rule). */
+int nvfp4_quantize_f16(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream);
+int nvfp4_quantize_bf16(const void* x, void* packed, void* sf_sw, int rows, int K, int L, void* stream);
 
 /* Last device-side status code of device `dev` (0 = none); clear != 0 resets it.
  * Call after synchronising the stream.  No counterpart in the reference, whose kernels spin

@@ -38,3 +38,19 @@ def test_quantized_operands_feed_the_gemm(oracle):
     torch.cuda.synchronize()
     want = torch.from_numpy(oracle.c_gemm(*gemm_oracle_args(data)))
     assert check.verbose_allclose(torch.from_numpy(out_np(c)), want, rtol=1e-3, atol=1e-3) == []
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("L,rows,K", [(1, 128, 256), (2, 200, 320), (1, 3, 16), (1, 512, 2048)])
+def test_half_precision_inputs_quantise_like_their_fp32_value(dtype, L, rows, K):
+    """fp16 / bf16 activations: widening to fp32 is exact, so the result must equal quantising x.float()."""
+    from eval_test_b200 import quantize
+    g = torch.Generator(device="cuda").manual_seed(7 * rows + K)
+    x = (torch.randn((L, rows, K), generator=g, device="cuda") * 3).to(dtype)
+    x[0, 0, :16] = 0
+    x[0, -1, -16:] = 6e4 if dtype == torch.float16 else 3e38    # scale saturates
+    op, sf, sf_p = quantize.quantize_operand(x)
+    op32, sf32, sf_p32 = quantize.quantize_operand(x.float())
+    assert torch.equal(op.view(torch.uint8), op32.view(torch.uint8))
+    assert torch.equal(sf.view(torch.uint8), sf32.view(torch.uint8))
+    assert torch.equal(sf_p.view(torch.uint8), sf_p32.view(torch.uint8))
