@@ -68,6 +68,9 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_gemm.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, f, vp]
     lib.nvfp4_dual_gemm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp]
     lib.nvfp4_dual_gemm_nvfp4.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, f, vp]
+    pp = ctypes.POINTER(ctypes.c_void_p)
+    lib.nvfp4_gemm_allgather.argtypes = [vp, vp, vp, vp, pp, i, i, i, i, i, i, f, vp]
+    lib.nvfp4_dual_gemm_allgather.argtypes = [vp, vp, vp, vp, vp, vp, pp, i, i, i, i, i, i, f, vp]
     lib.nvfp4_grouped_gemm.argtypes = [ctypes.POINTER(Group), i, f, vp]
     lib.nvfp4_grouped_gemm_noalloc.argtypes = [ctypes.POINTER(Group), i, f, vp]
     for q in (lib.nvfp4_quantize_f32, lib.nvfp4_quantize_f16, lib.nvfp4_quantize_bf16):
@@ -76,7 +79,7 @@ def load() -> ctypes.CDLL:
     lib.nvfp4_wait_selftest.argtypes = [i, ctypes.POINTER(ctypes.c_double), vp]
     lib.nvfp4_strerror.argtypes = [i]
     lib.nvfp4_strerror.restype = ctypes.c_char_p
-    for name in ("nvfp4_gemv", "nvfp4_gemm", "nvfp4_dual_gemm", "nvfp4_dual_gemm_nvfp4", "nvfp4_grouped_gemm", "nvfp4_grouped_gemm_noalloc", "nvfp4_quantize_f32", "nvfp4_quantize_f16", "nvfp4_quantize_bf16", "nvfp4_device_status",
+    for name in ("nvfp4_gemv", "nvfp4_gemm", "nvfp4_dual_gemm", "nvfp4_dual_gemm_nvfp4", "nvfp4_gemm_allgather", "nvfp4_dual_gemm_allgather", "nvfp4_grouped_gemm", "nvfp4_grouped_gemm_noalloc", "nvfp4_quantize_f32", "nvfp4_quantize_f16", "nvfp4_quantize_bf16", "nvfp4_device_status",
                  "nvfp4_wait_selftest", "nvfp4_abi_version", "nvfp4_shutdown"):
         getattr(lib, name).restype = i
     _lib = lib

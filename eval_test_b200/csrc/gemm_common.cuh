@@ -28,6 +28,16 @@ struct alignas(64) GroupEntry {
     int tiles_m, tiles_n;
 };
 
+// Fused all-gather of an N-sharded GEMM: every output chunk is stored into the full C buffer of every rank (peer
+// memory mapped into this process, plain stores).  d[w] = byte distance of rank w's buffer from buffer 0.
+struct GatherOut {
+    int n = 0;                  // ranks (0: not a gathering launch)
+    int ldc = 0;                // row pitch of the full C in elements (N of all ranks together)
+    int col0 = 0;               // first column of this rank's slice
+    long long d[8] = {};
+    __half* c0 = nullptr;       // buffer 0
+};
+
 struct GemmParams {
     const uint8_t* sfa;   // swizzled scales of A  [L][ceil(M/128)][K/64][512]
     const uint8_t* sfb;   // swizzled scales of B (B1 for the dual GEMM)
@@ -35,6 +45,7 @@ struct GemmParams {
     __half* c;            // [L][M][N]
     uint8_t* cq = nullptr;   // NVFP4 output instead of fp16: packed e2m1 [L][M][N/2] ...
     uint8_t* sfc = nullptr;  // ... and its block scales, swizzled [L][ceil(M/128)][N/64][512]
+    GatherOut gather;
     int M, N, K, L;
     float alpha;
     int* status;
@@ -136,9 +147,9 @@ __device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUt
 
 // fp32 accumulator chunk(s) -> 32 fp16 outputs of one row, written as two whole 32-byte sectors
 // (16-byte stores left half-written sectors behind and cost 35 us at 8192^3).
-template <bool DUAL>
+template <bool DUAL, bool GATHER = false>
 __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32], const uint32_t (&w)[32], float alpha,
-                                            bool pred) {
+                                            bool pred, const GatherOut* go = nullptr) {
     uint32_t o[16];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
@@ -157,8 +168,17 @@ __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32]
         const uint32_t hi[8] = {o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]};
         // written once, never read by this kernel: evict-first keeps the operands in L2 instead
         const uint64_t pol = policy_evict_first();
-        st_global_256_hint(dst, lo, pol);
-        st_global_256_hint(dst + 16, hi, pol);
+        if (GATHER) {
+            // dst addresses buffer 0; the same 64 bytes go to every rank's buffer (the local one among them)
+            for (int r = 0; r < go->n; r++) {
+                __half* q = reinterpret_cast<__half*>(reinterpret_cast<char*>(dst) + go->d[r]);
+                st_global_256_hint(q, lo, pol);
+                st_global_256_hint(q + 16, hi, pol);
+            }
+        } else {
+            st_global_256_hint(dst, lo, pol);
+            st_global_256_hint(dst + 16, hi, pol);
+        }
     }
 }
 
@@ -201,9 +221,11 @@ __device__ __forceinline__ void store_chunk_q(QuantOut& q, int cc, const uint32_
 // for those loads, not for the conversion and stores.
 // CLUSTER: ovl_free is a shared::cluster address (the barrier may live in the peer CTA).
 // QOUT: NVFP4 output through q instead of fp16 through crow.
-template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false>
+// GATHER: fp16 output to every rank's buffer (crow addresses buffer 0).
+template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false, bool GATHER = false>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, bool row_ok, int n0, int N, float alpha,
-                                              uint32_t ovl_free, int lane, QuantOut* q = nullptr) {
+                                              uint32_t ovl_free, int lane, QuantOut* q = nullptr,
+                                              const GatherOut* go = nullptr) {
     constexpr int NCH = BN / 32;
     uint32_t ov[OVC > 0 ? OVC : 1][32];
     if (OVC > 0) {
@@ -232,9 +254,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, boo
             store_chunk_q<DUAL>(*q, cc, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
                                 w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
                                 pred);
-        else store_chunk<DUAL>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+        else store_chunk<DUAL, GATHER>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
                           w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
-                          pred);
+                          pred, go);
     }
 }
 

@@ -38,7 +38,8 @@ namespace nvfp4 {
 
 // BN: output columns per tile (GEMM: 128 or 256; DUAL: 128, the MMA is 256 wide over [B1;B2]).
 // QOUT: the epilogue writes NVFP4 (packed codes + swizzled block scales) instead of fp16.
-template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false>
+// GATHER: the fp16 output goes to the full C buffer of every rank of an N-sharded run (fused all-gather).
+template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false, bool GATHER = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
             const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
@@ -226,7 +227,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tc_fence_after_sync();
             const uint32_t t_lane = tmem_base + buf * ACC1_OFF + ((uint32_t)(q * 32) << 16);
             const int srow = row < ti.M ? row : 0;
-            __half* crow = ti.c + (size_t)srow * ti.N + n0;
+            __half* crow = GATHER ? p.gather.c0 + ((size_t)ti.l * ti.M + srow) * p.gather.ldc + p.gather.col0 + n0
+                                  : ti.c + (size_t)srow * ti.N + n0;
             QuantOut qo;
             if (QOUT) {
                 const size_t grow = (size_t)ti.l * ti.M + srow;                       // row of the [L*M][N] output
@@ -236,11 +238,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
             // buffer 0 shares its last OVERLAP columns, buffer 1 its first
             if (buf == 0)
-                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS, false, QOUT>(t_lane, crow, row < ti.M, n0, ti.N,
-                                                                                   p.alpha, ovl_free, lane, &qo);
+                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS, false, QOUT, GATHER>(
+                    t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free, lane, &qo, &p.gather);
             else
-                epilogue_tile<BN, DUAL, 0, OV_CHUNKS, false, QOUT>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free,
-                                                                  lane, &qo);
+                epilogue_tile<BN, DUAL, 0, OV_CHUNKS, false, QOUT, GATHER>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha,
+                                                                          ovl_free, lane, &qo, &p.gather);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
@@ -287,14 +289,14 @@ int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L
     return NVFP4_OK;
 }
 
-template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false>
+template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false, bool GATHER = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                        cudaStream_t stream) {
     constexpr int MMA_N = DUAL ? 2 * BN : BN;
     constexpr size_t STAGE = 128 * 128 + MMA_N * 128 + 2048 + (MMA_N / 128) * 2048;
     constexpr size_t SMEM = STAGES * STAGE + 1024;  // + slack for the 1024-byte alignment
     static_assert(SMEM <= 227 * 1024 - 256, "shared memory");
-    auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES, QOUT>;
+    auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES, QOUT, GATHER>;
     static bool configured[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
@@ -425,6 +427,76 @@ extern "C" int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* 
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N / 128) * L;
     return launch_gemm<128, true, false, 4, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
+}
+
+// Fills the gather description of a launch from the ranks' buffer addresses.
+static int fill_gather(GatherOut& g, void* const* c_all, int world, int rank, int N_local) {
+    if (!c_all) return NVFP4_ERR_NULL;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return NVFP4_ERR_SHAPE;
+    for (int r = 0; r < world; r++) {
+        if (!c_all[r]) return NVFP4_ERR_NULL;
+        if ((uintptr_t)c_all[r] & 31) return NVFP4_ERR_ALIGN;
+        g.d[r] = (long long)((intptr_t)c_all[r] - (intptr_t)c_all[0]);
+    }
+    g.n = world; g.ldc = N_local * world; g.col0 = rank * N_local; g.c0 = (__half*)c_all[0];
+    return NVFP4_OK;
+}
+
+extern "C" int nvfp4_gemm_allgather(const void* a, const void* b, const void* sfa_sw, const void* sfb_sw,
+                                    void* const* c_all, int world, int rank, int M, int N_local, int K, int L,
+                                    float alpha, void* stream) {
+    const void* ptrs[5] = {a, b, sfa_sw, sfb_sw, c_all ? c_all[0] : nullptr};
+    int rc = check_common(ptrs, 5, M, N_local, K, L);
+    if (rc) return rc;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    GemmParams p;
+    rc = fill_gather(p.gather, c_all, world, rank, N_local);
+    if (rc) return rc;
+    const long tiles256 = (long)((M + 127) / 128) * (N_local / 256) * L;
+    const bool wide = (N_local % 256 == 0) && tiles256 >= sm_count(dev);
+    CUtensorMap ta, tb;
+    rc = make_operand_tmap(&ta, a, M, K, L, 128);
+    if (rc) return rc;
+    rc = make_operand_tmap(&tb, b, N_local, K, L, wide ? 256 : 128);
+    if (rc) return rc;
+    p.sfa = (const uint8_t*)sfa_sw; p.sfb = (const uint8_t*)sfb_sw; p.sfb2 = nullptr; p.c = nullptr;
+    p.M = M; p.N = N_local; p.K = K; p.L = L; p.alpha = alpha;
+    p.status = status_word(dev);
+    p.budget_ns = wait_budget_ns();
+    p.table = nullptr; p.G = 0;
+    p.total_tiles = ((M + BM - 1) / BM) * (N_local / (wide ? 256 : 128)) * L;
+    if (wide) return launch_gemm<256, false, false, 4, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
+    return launch_gemm<128, false, false, 6, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
+}
+
+extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const void* b2, const void* sfa_sw,
+                                         const void* sfb1_sw, const void* sfb2_sw, void* const* c_all, int world,
+                                         int rank, int M, int N_local, int K, int L, float alpha, void* stream) {
+    const void* ptrs[7] = {a, b1, b2, sfa_sw, sfb1_sw, sfb2_sw, c_all ? c_all[0] : nullptr};
+    int rc = check_common(ptrs, 7, M, N_local, K, L);
+    if (rc) return rc;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    GemmParams p;
+    rc = fill_gather(p.gather, c_all, world, rank, N_local);
+    if (rc) return rc;
+    CUtensorMap ta, tb1, tb2;
+    rc = make_operand_tmap(&ta, a, M, K, L, 128);
+    if (rc) return rc;
+    rc = make_operand_tmap(&tb1, b1, N_local, K, L, 128);
+    if (rc) return rc;
+    rc = make_operand_tmap(&tb2, b2, N_local, K, L, 128);
+    if (rc) return rc;
+    p.sfa = (const uint8_t*)sfa_sw; p.sfb = (const uint8_t*)sfb1_sw; p.sfb2 = (const uint8_t*)sfb2_sw; p.c = nullptr;
+    p.M = M; p.N = N_local; p.K = K; p.L = L; p.alpha = alpha;
+    p.status = status_word(dev);
+    p.budget_ns = wait_budget_ns();
+    p.table = nullptr; p.G = 0;
+    p.total_tiles = ((M + BM - 1) / BM) * (N_local / 128) * L;
+    return launch_gemm<128, true, false, 4, false, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------------ grouped GEMM

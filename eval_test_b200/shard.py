@@ -107,3 +107,72 @@ def gather_rows(c_local: torch.Tensor, world: int) -> torch.Tensor:
     parts = [torch.empty_like(flat) for _ in range(world)]
     dist.all_gather(parts, flat)
     return F.batch_last(torch.cat(parts, dim=1).contiguous())
+
+
+# ----------------------------------------------------------------------------------------------- fused all-gather
+class GatheredOutput:
+    """The full ``[M, N, L]`` fp16 output of an N-sharded GEMM, one copy per rank, that every rank's kernel writes its
+    column slice into directly (``nvfp4_gemm_allgather``): a symmetric-memory buffer whose copies on the other ranks
+    are mapped into this process.  ``ptrs`` may also be given explicitly (buffers of one device: single-GPU tests)."""
+
+    def __init__(self, m: int, n: int, l: int, device, group=None, ptrs=None, buf=None):
+        self.m, self.n, self.l = m, n, l
+        if ptrs is not None:
+            self.buf, self.ptrs, self.group = buf, list(ptrs), None
+        else:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.group = group if group is not None else dist.group.WORLD
+            self.buf = symm_mem.empty((l, m, n), dtype=torch.float16, device=device)
+            self.handle = symm_mem.rendezvous(self.buf, self.group)
+            self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        self.world = len(self.ptrs)
+
+    def view(self) -> torch.Tensor:
+        """The local copy as ``[M, N, L]`` (the layout of the reference's ``c``)."""
+        return F.batch_last(self.buf)
+
+    def wait_all(self):
+        """Stream-ordered: every rank's kernel has finished, so every copy is complete."""
+        if self.group is not None and self.world > 1:
+            dist.barrier(group=self.group)
+
+
+def _ptr_array(ptrs):
+    import ctypes
+    return (ctypes.c_void_p * len(ptrs))(*ptrs)
+
+
+def gemm_allgather(shard, out: GatheredOutput, rank: int, alpha: float = 1.0):
+    """``shard``: this rank's tuple from ``shard_gemm`` (its ``c`` is not used).  Writes the rank's columns into every
+    rank's copy of ``out``; call ``out.wait_all()`` before reading."""
+    from . import _args, _lib
+    a, b, _, _, sfa_p, sfb_p, _ = shard
+    m, k2, l = a.shape
+    n_loc, k = b.shape[0], 2 * k2
+    if (m, n_loc * out.world, l) != (out.m, out.n, out.l):
+        raise ValueError(f"gemm_allgather: shard {m} x {n_loc} x {l} does not tile an output {out.m} x {out.n} x {out.l} "
+                         f"over {out.world} ranks")
+    with torch.cuda.device(a.device):
+        code = _lib.load().nvfp4_gemm_allgather(
+            _args.operand_ptr(a, m, k2, l, "a"), _args.operand_ptr(b, n_loc, k2, l, "b"),
+            _args.scales_ptr(sfa_p, m, k, l, "sfa_permuted"), _args.scales_ptr(sfb_p, n_loc, k, l, "sfb_permuted"),
+            _ptr_array(out.ptrs), out.world, rank, m, n_loc, k, l, float(alpha), _args.stream_ptr(a.device))
+    _lib.check(code, "nvfp4_gemm_allgather")
+    return out
+
+
+def dual_gemm_allgather(shard, out: GatheredOutput, rank: int, alpha: float = 1.0):
+    from . import _args, _lib
+    a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, _ = shard
+    m, k2, l = a.shape
+    n_loc, k = b1.shape[0], 2 * k2
+    if (m, n_loc * out.world, l) != (out.m, out.n, out.l):
+        raise ValueError("dual_gemm_allgather: the shard does not tile the output")
+    with torch.cuda.device(a.device):
+        code = _lib.load().nvfp4_dual_gemm_allgather(
+            _args.operand_ptr(a, m, k2, l, "a"), _args.operand_ptr(b1, n_loc, k2, l, "b1"),
+            _args.operand_ptr(b2, n_loc, k2, l, "b2"), _args.scales_ptr(sfa_p, m, k, l, "sfa_permuted"),
+            _args.scales_ptr(sfb1_p, n_loc, k, l, "sfb1_permuted"), _args.scales_ptr(sfb2_p, n_loc, k, l, "sfb2_permuted"),
+            _ptr_array(out.ptrs), out.world, rank, m, n_loc, k, l, float(alpha), _args.stream_ptr(a.device))
+    _lib.check(code, "nvfp4_dual_gemm_allgather")
+    return out

@@ -73,6 +73,19 @@ int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const v
                           const void* sfb1_sw, const void* sfb2_sw, void* c_packed, void* sfc_sw,
                           int M, int N, int K, int L, float alpha, void* stream);
 
+/* N-sharded GEMM / dual GEMM with the all-gather of the output fused into the epilogue: this rank computes the
+ * columns [rank*N_local, (rank+1)*N_local) of C and stores every piece of them into the full C buffer
+ * [L][M][N_local*world] of EVERY rank: c_all[r] is rank r's buffer as mapped into this process (peer memory:
+ * symmetric memory or an IPC mapping; c_all[rank] is the local one), 32-byte aligned; world <= 8.  Plain stores over
+ * NVLink, no collective call; the caller orders "all ranks have finished" (a barrier on the stream) before C is read.
+ * No counterpart in the reference (a single-GPU harness); replaces gemm + ncclAllGather of the column shards. */
+int nvfp4_gemm_allgather(const void* a, const void* b, const void* sfa_sw, const void* sfb_sw,
+                         void* const* c_all, int world, int rank, int M, int N_local, int K, int L,
+                         float alpha, void* stream);
+int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const void* b2, const void* sfa_sw,
+                              const void* sfb1_sw, const void* sfb2_sw, void* const* c_all, int world,
+                              int rank, int M, int N_local, int K, int L, float alpha, void* stream);
+
 /* One problem of a grouped GEMM (L = 1): c[M][N] = fp16(alpha * (a*sfa) @ (b*sfb)^T). */
 typedef struct nvfp4_group {
     const void* a;       /* [M][K/2] */
