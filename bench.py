@@ -178,6 +178,59 @@ class GemmWorkload:
         return O.c_gemm(*args)
 
 
+class GemmGatherWorkload(GemmWorkload):
+    """The same N-sharded GEMM with the full C assembled on every rank inside the timed step: either the kernel's
+    fused all-gather epilogue (stores into every rank's copy over NVLink, then a barrier) or the kernel followed by
+    an NCCL all-gather of the column shards.  The roofline target is the slower of the rank's flops at the tensor
+    peak and the bytes the rank must send at 770 GB/s (measured peer-copy bandwidth per direction)."""
+    metric = "nvfp4_gemm_allgather_tflops"
+    nvlink_gbs = 770.0
+
+    def __init__(self, fused=True, m=8192, n=8192, k=8192):
+        super().__init__(m, n, k)
+        self.fused = fused
+        self.name = f"gemm_m{m}_n{n}_k{k}_allgather_{'fused' if fused else 'nccl'}"
+
+    def small(self):
+        return GemmGatherWorkload(self.fused, m=4096, n=8192, k=4096)
+
+    def make(self, rank, world, device):
+        import torch
+        from eval_test_b200 import shard
+        data = super().make(rank, world, device)
+        self.rank, self.world = rank, world
+        if self.fused:
+            if world > 1:
+                self.out = shard.GatheredOutput(self.m, self.n, 1, device)
+            else:
+                buf = torch.empty((1, self.m, self.n), dtype=torch.float16, device=device)
+                self.out = shard.GatheredOutput(self.m, self.n, 1, device, ptrs=[buf.data_ptr()], buf=buf)
+        return data
+
+    def run(self, data):
+        from eval_test_b200 import nvfp4_gemm, shard
+        if self.fused:
+            shard.gemm_allgather(data, self.out, self.rank, alpha=self.alpha)
+            self.out.wait_all()
+            return self.out.view()
+        return shard.gather_cols(nvfp4_gemm.custom_kernel(data, alpha=self.alpha), self.world)
+
+    def io(self, data):
+        ins, outs = super().io(data)
+        return ins, ([self.out.buf] if self.fused else outs)
+
+    def config(self, world):
+        cfg = super().config(world)
+        cfg["sharding"] = ("columns of C per rank; every rank ends with the full C: " +
+                           ("fused all-gather epilogue (peer stores) + barrier" if self.fused
+                            else "kernel, then NCCL all-gather of the shards"))
+        return cfg
+
+    def target_us(self, world, tensor_peak_tflops):
+        send = 2 * self.m * (self.n // world) * (world - 1)
+        return max(self.work(world) / (tensor_peak_tflops * 1e12), send / (self.nvlink_gbs * 1e9)) * 1e6
+
+
 class DualGemmWorkload(GemmWorkload):
     """SwiGLU up-projection: C = silu(A.B1) * (A.B2), A 4096 x 4096, B1 and B2 14336 x 4096."""
     name = "dual_gemm_m4096_n14336_k4096"
@@ -408,6 +461,7 @@ class QuantizeWorkload:
 
 WORKLOADS = {"gemv": GemvWorkload, "gemm": GemmWorkload, "dual_gemm": DualGemmWorkload,
              "dual_gemm_nvfp4": DualGemmNvfp4Workload,
+             "gemm_gather_fused": lambda: GemmGatherWorkload(True), "gemm_gather_nccl": lambda: GemmGatherWorkload(False),
              "grouped_gemm": GroupedGemmWorkload, "quantize": QuantizeWorkload}
 
 
@@ -659,6 +713,10 @@ def main():
                     "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks.summary(),
         }
+        if hasattr(wl, "target_us"):   # compute + collective: achieved time against the slower of the two floors
+            tgt = wl.target_us(world, peak)
+            line["roofline"].update({"bound": "tensor or nvlink", "target_us": tgt, "frac": tgt / (kern_ms * 1e3),
+                                     "nvlink_gbs": wl.nvlink_gbs})
         traffic = ROOT / "profiles" / "traffic.json"
         if traffic.exists():
             try:

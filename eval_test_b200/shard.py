@@ -124,7 +124,10 @@ class GatheredOutput:
             self.group = group if group is not None else dist.group.WORLD
             self.buf = symm_mem.empty((l, m, n), dtype=torch.float16, device=device)
             self.handle = symm_mem.rendezvous(self.buf, self.group)
-            self.ptrs = [int(p) for p in self.handle.buffer_ptrs]
+            # the handle lists each rank's symmetric buffer; this tensor may start at an offset inside it
+            base = [int(p) for p in self.handle.buffer_ptrs]
+            off = self.buf.data_ptr() - base[self.handle.rank]
+            self.ptrs = [p + off for p in base]
         self.world = len(self.ptrs)
 
     def view(self) -> torch.Tensor:
