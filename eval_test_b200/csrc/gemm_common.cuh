@@ -38,6 +38,15 @@ struct GatherOut {
     __half* c0 = nullptr;       // buffer 0
 };
 
+// What one epilogue warp needs for a gathering store: the launch's description, 4 KB of shared memory of its own
+// and how many of its 32 rows exist.
+struct GatherCtx {
+    const GatherOut* g;
+    uint4* stage;      // 4 KB: 32 rows x 128 bytes
+    int rows;
+    int cc;            // chunk of the tile being stored
+};
+
 struct GemmParams {
     const uint8_t* sfa;   // swizzled scales of A  [L][ceil(M/128)][K/64][512]
     const uint8_t* sfb;   // swizzled scales of B (B1 for the dual GEMM)
@@ -147,9 +156,12 @@ __device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUt
 
 // fp32 accumulator chunk(s) -> 32 fp16 outputs of one row, written as two whole 32-byte sectors
 // (16-byte stores left half-written sectors behind and cost 35 us at 8192^3).
+// GATHER: dst is the warp's first row (the same pointer in every lane) in buffer 0 and pred only says that the
+// columns exist.  The warp's rows are turned through shared memory so that the pieces that cross NVLink are whole
+// 128-byte lines instead of 32 separate 32-byte pieces per instruction.
 template <bool DUAL, bool GATHER = false>
 __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32], const uint32_t (&w)[32], float alpha,
-                                            bool pred, const GatherOut* go = nullptr) {
+                                            bool pred, const GatherCtx* gc = nullptr) {
     uint32_t o[16];
 #pragma unroll
     for (int i = 0; i < 16; i++) {
@@ -163,22 +175,39 @@ __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32]
         }
         o[i] = *reinterpret_cast<uint32_t*>(&h);
     }
+    if (GATHER) {
+        // Two chunks (128 bytes of every row) are collected in the warp's 4 KB before they go out: a store
+        // instruction then writes 4 rows x 128 contiguous bytes.  16-byte pieces are XOR-swizzled by the row so
+        // that both the row-wise writes and the transposed reads use every bank.
+        const int lane = threadIdx.x & 31;
+        uint4* st = gc->stage;
+        const int half = gc->cc & 1;
+#pragma unroll
+        for (int j = 0; j < 4; j++)
+            st[lane * 8 + ((4 * half + j) ^ (lane & 7))] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
+        if (!half) return;
+        __syncwarp();
+        const GatherOut& g = *gc->g;
+#pragma unroll
+        for (int it = 0; it < 8; it++) {
+            const int r = it * 4 + (lane >> 3), pc = lane & 7;
+            const uint4 val = st[r * 8 + (pc ^ (r & 7))];
+            if (pred && r < gc->rows) {
+                // dst is this (odd) chunk's column; the pair starts 32 columns = 64 bytes before it
+                char* q0 = reinterpret_cast<char*>(dst) - 64 + (size_t)r * g.ldc * 2 + pc * 16;
+                for (int k = 0; k < g.n; k++) *reinterpret_cast<uint4*>(q0 + g.d[k]) = val;   // every rank's buffer
+            }
+        }
+        __syncwarp();
+        return;
+    }
     if (pred) {
         const uint32_t lo[8] = {o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]};
         const uint32_t hi[8] = {o[8], o[9], o[10], o[11], o[12], o[13], o[14], o[15]};
         // written once, never read by this kernel: evict-first keeps the operands in L2 instead
         const uint64_t pol = policy_evict_first();
-        if (GATHER) {
-            // dst addresses buffer 0; the same 64 bytes go to every rank's buffer (the local one among them)
-            for (int r = 0; r < go->n; r++) {
-                __half* q = reinterpret_cast<__half*>(reinterpret_cast<char*>(dst) + go->d[r]);
-                st_global_256_hint(q, lo, pol);
-                st_global_256_hint(q + 16, hi, pol);
-            }
-        } else {
-            st_global_256_hint(dst, lo, pol);
-            st_global_256_hint(dst + 16, hi, pol);
-        }
+        st_global_256_hint(dst, lo, pol);
+        st_global_256_hint(dst + 16, hi, pol);
     }
 }
 
@@ -221,11 +250,11 @@ __device__ __forceinline__ void store_chunk_q(QuantOut& q, int cc, const uint32_
 // for those loads, not for the conversion and stores.
 // CLUSTER: ovl_free is a shared::cluster address (the barrier may live in the peer CTA).
 // QOUT: NVFP4 output through q instead of fp16 through crow.
-// GATHER: fp16 output to every rank's buffer (crow addresses buffer 0).
+// GATHER: fp16 output to every rank's buffer (crow: the warp's first row in buffer 0, see store_chunk).
 template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false, bool GATHER = false>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, bool row_ok, int n0, int N, float alpha,
                                               uint32_t ovl_free, int lane, QuantOut* q = nullptr,
-                                              const GatherOut* go = nullptr) {
+                                              const GatherCtx* gc = nullptr) {
     constexpr int NCH = BN / 32;
     uint32_t ov[OVC > 0 ? OVC : 1][32];
     if (OVC > 0) {
@@ -248,15 +277,18 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, boo
         if (!v_pre) tc_ld_32x32(t_lane + cc * 32, v);
         if (DUAL && !w_pre) tc_ld_32x32(t_lane + (cc + YOFF) * 32, w);
         if (!v_pre || (DUAL && !w_pre)) tc_wait_ld();
-        const bool pred = row_ok && n0 + cc * 32 < N;
+        const bool pred = (GATHER || row_ok) && n0 + cc * 32 < N;
         // (index clamps only keep the never-taken branch in range for the compiler)
         if (QOUT)
             store_chunk_q<DUAL>(*q, cc, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
                                 w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
                                 pred);
-        else store_chunk<DUAL, GATHER>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+        else {
+            if (GATHER) const_cast<GatherCtx*>(gc)->cc = cc;
+            store_chunk<DUAL, GATHER>(crow + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
                           w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,
-                          pred, go);
+                          pred, gc);
+        }
     }
 }
 

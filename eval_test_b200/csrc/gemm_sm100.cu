@@ -227,8 +227,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tc_fence_after_sync();
             const uint32_t t_lane = tmem_base + buf * ACC1_OFF + ((uint32_t)(q * 32) << 16);
             const int srow = row < ti.M ? row : 0;
-            __half* crow = GATHER ? p.gather.c0 + ((size_t)ti.l * ti.M + srow) * p.gather.ldc + p.gather.col0 + n0
+            const int wrow0 = ti.m0 + q * 32;          // first row of this warp
+            __half* crow = GATHER ? p.gather.c0 + ((size_t)ti.l * ti.M + wrow0) * p.gather.ldc + p.gather.col0 + n0
                                   : ti.c + (size_t)srow * ti.N + n0;
+            GatherCtx gc;
+            if (GATHER) {
+                gc.g = &p.gather;
+                gc.stage = reinterpret_cast<uint4*>(smem_raw + (smem0 - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) + (warp - 2) * 256;
+                gc.rows = min(32, ti.M - wrow0);
+            }
             QuantOut qo;
             if (QOUT) {
                 const size_t grow = (size_t)ti.l * ti.M + srow;                       // row of the [L*M][N] output
@@ -239,10 +246,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             // buffer 0 shares its last OVERLAP columns, buffer 1 its first
             if (buf == 0)
                 epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS, false, QOUT, GATHER>(
-                    t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free, lane, &qo, &p.gather);
+                    t_lane, crow, row < ti.M, n0, ti.N, p.alpha, ovl_free, lane, &qo, &gc);
             else
                 epilogue_tile<BN, DUAL, 0, OV_CHUNKS, false, QOUT, GATHER>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha,
-                                                                          ovl_free, lane, &qo, &p.gather);
+                                                                          ovl_free, lane, &qo, &gc);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
@@ -294,7 +301,8 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
                        cudaStream_t stream) {
     constexpr int MMA_N = DUAL ? 2 * BN : BN;
     constexpr size_t STAGE = 128 * 128 + MMA_N * 128 + 2048 + (MMA_N / 128) * 2048;
-    constexpr size_t SMEM = STAGES * STAGE + 1024;  // + slack for the 1024-byte alignment
+    // + slack for the 1024-byte alignment (+ 4 KB per epilogue warp to turn chunks for the gathering stores)
+    constexpr size_t SMEM = STAGES * STAGE + 1024 + (GATHER ? 4 * 4096 : 0);
     static_assert(SMEM <= 227 * 1024 - 256, "shared memory");
     auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES, QOUT, GATHER>;
     static bool configured[64] = {};
@@ -467,8 +475,9 @@ extern "C" int nvfp4_gemm_allgather(const void* a, const void* b, const void* sf
     p.budget_ns = wait_budget_ns();
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N_local / (wide ? 256 : 128)) * L;
-    if (wide) return launch_gemm<256, false, false, 4, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
-    return launch_gemm<128, false, false, 6, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
+    // one stage less than the plain kernels: the room goes to the epilogue warps' store staging
+    if (wide) return launch_gemm<256, false, false, 3, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
+    return launch_gemm<128, false, false, 5, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
 }
 
 extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const void* b2, const void* sfa_sw,
@@ -496,7 +505,7 @@ extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const vo
     p.budget_ns = wait_budget_ns();
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N_local / 128) * L;
-    return launch_gemm<128, true, false, 4, false, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
+    return launch_gemm<128, true, false, 3, false, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
 }
 
 // ------------------------------------------------------------------------------------------ grouped GEMM

@@ -135,9 +135,12 @@ class GatheredOutput:
         return F.batch_last(self.buf)
 
     def wait_all(self):
-        """Stream-ordered: every rank's kernel has finished, so every copy is complete."""
+        """Stream-ordered: what follows on the current stream runs after every rank's kernel has finished, so every
+        copy is complete.  (A one-element all-reduce: unlike ``dist.barrier`` it does not block the host.)"""
         if self.group is not None and self.world > 1:
-            dist.barrier(group=self.group)
+            if getattr(self, "_flag", None) is None:
+                self._flag = torch.zeros(1, dtype=torch.float32, device=self.buf.device)
+            dist.all_reduce(self._flag, group=self.group)
 
 
 def _ptr_array(ptrs):
