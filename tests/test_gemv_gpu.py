@@ -153,3 +153,29 @@ def test_wait_selftest_expires_and_reports():
     assert _lib.device_status(torch.cuda.current_device()) == 105
     assert _lib.device_status(torch.cuda.current_device()) == 0
     assert float(torch.ones(4, device="cuda").sum()) == 4.0
+
+
+def test_two_streams_at_once(monkeypatch):
+    """Launches of the tensor-core kernel that overlap on two streams (each grid hands out its own tiles through
+    cluster launch control; nothing is shared between launches) give the bits of the same launches run alone."""
+    from eval_test_b200 import _lib, inputs, nvfp4_gemv
+    monkeypatch.setenv("NVFP4_GEMV_PATH", "tensor")
+    d1 = inputs.gemv_quantized(128 * 60, 4096, 1, seed=41, device="cuda")     # 60 tiles: leaves SMs for the other launch
+    d2 = inputs.gemv_quantized(128 * 50, 2048, 2, seed=42, device="cuda")
+    want1 = nvfp4_gemv.custom_kernel(d1).clone()
+    want2 = nvfp4_gemv.custom_kernel(d2).clone()
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    for _ in range(20):
+        d1[-1].zero_(); d2[-1].zero_()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(s1):
+            for _ in range(3):
+                nvfp4_gemv.custom_kernel(d1)
+        with torch.cuda.stream(s2):
+            for _ in range(3):
+                nvfp4_gemv.custom_kernel(d2)
+        torch.cuda.synchronize()
+        assert torch.equal(d1[-1].view(torch.int16), want1.view(torch.int16))
+        assert torch.equal(d2[-1].view(torch.int16), want2.view(torch.int16))
+    assert _lib.device_status(torch.cuda.current_device()) == 0
