@@ -456,6 +456,9 @@ extern "C" int nvfp4_gemm_allgather(const void* a, const void* b, const void* sf
     const void* ptrs[5] = {a, b, sfa_sw, sfb_sw, c_all ? c_all[0] : nullptr};
     int rc = check_common(ptrs, 5, M, N_local, K, L);
     if (rc) return rc;
+    // one rank: nothing to gather, and the plain epilogue is the faster one for local memory (measured at 8192^3:
+    // 223 us against 300 us through the staged stores)
+    if (world == 1 && rank == 0 && c_all) return nvfp4_gemm(a, b, sfa_sw, sfb_sw, c_all[0], M, N_local, K, L, alpha, stream);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
@@ -486,6 +489,8 @@ extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const vo
     const void* ptrs[7] = {a, b1, b2, sfa_sw, sfb1_sw, sfb2_sw, c_all ? c_all[0] : nullptr};
     int rc = check_common(ptrs, 7, M, N_local, K, L);
     if (rc) return rc;
+    if (world == 1 && rank == 0 && c_all)
+        return nvfp4_dual_gemm(a, b1, b2, sfa_sw, sfb1_sw, sfb2_sw, c_all[0], M, N_local, K, L, alpha, stream);
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
