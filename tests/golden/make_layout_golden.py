@@ -1,8 +1,8 @@
 """Generates ``layout_golden.npz``: the scale-factor layout as produced by the REFERENCE's own code.
 
-Run in a container that has the reference checkout (it cannot travel to the GPU box):
+Run where a checkout of the reference is at hand:
 
-    python tests/golden/make_layout_golden.py /root/reference
+    python tests/golden/make_layout_golden.py <path of the reference checkout>
 
 It imports ``to_blocked`` (eval/common/scale_helpers.py:10-17) and the padded variant of the grouped task
 (eval/nvfp4_grouped_gemm/reference.py:14-36), feeds them seeded row-major scale matrices and stores inputs and
@@ -52,4 +52,6 @@ def main(ref_root: str):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_layout_golden.py <path of the reference checkout>")
+    main(sys.argv[1])
