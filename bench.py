@@ -3,19 +3,26 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
 
-One "step" is one pass of the hot path over one batch of synthetic input.  The default workload is the
-batched GEMV the headline metric is quoted on (M = K = 16384, L = 4, N(0,1) data through the block-16
-quantiser): HBM-bound, reported in GB/s of algorithmic bytes.  With N > 1 (launched by torchrun, one process
-per GPU) every rank runs a shard of the same size (rows of A are independent, so nothing is exchanged): weak
-scaling, value = bytes of all ranks / max-over-ranks device time.
+One "step" is one pass of the hot path over one batch of synthetic input.  With no ``--workload`` the run prints ONE
+JSON line whose headline (``metric`` / ``value`` / ``roofline`` / ``e2e`` / ``cpu_baseline`` / ``clocks``) is the
+batched GEMV the metric is quoted on (M = K = 16384, L = 4, N(0,1) data through the block-16 quantiser, HBM-bound,
+GB/s of algorithmic bytes) and whose ``workloads`` object holds the same record for the other configurations: the
+8192^3 GEMM, the SwiGLU dual GEMM, the 64-group grouped GEMM with and without forced empty groups, and (N > 1) the
+GEMV split M/N ways.  ``--workload NAME`` measures one of them alone.
 
-The JSON line carries, besides the contract keys: ``roofline`` (dominant kernel, CUDA-event duration against
-the measured HBM peak), ``e2e`` (same metric through ``custom_kernel`` with pinned host inputs copied in and
-the output copied out inside the timed region), ``cpu_baseline`` (the CPU oracle on the host cores, rank 0,
-N = 1) and ``clocks`` (NVML samples taken during the timed region).
+N > 1 (torchrun, one process per GPU, no data-path collective): the headline GEMV is weak scaling (every rank owns
+16384 more rows); the sub-records are strong scaling - GEMM and dual GEMM split the columns of C (rows of B),
+the grouped GEMM deals whole groups to ranks balanced by weight bytes, the GEMV splits rows.  Every number is device
+time (CUDA events on the launching stream), maximum over ranks.
 
-``--impl reference`` times the CPU oracle (the reference has no CPU implementation of this path; the oracle is
-the restatement of it) with all host threads on a bounded sample of the same workload.
+Each record carries ``roofline`` (dominant kernel against the measured peak: copy bandwidth for the HBM-bound
+workloads, 4 x the bf16 GEMM burst rate for the tensor-bound ones, with the fraction of the nominal 8 TB/s /
+9 PFLOP/s beside it), ``e2e`` (the same metric through ``custom_kernel`` with pinned host inputs copied in and the
+output copied out inside the timed region), ``cpu_baseline`` (N = 1, rank 0: the CPU oracle on the host cores, two
+routes, see ``cpu_baseline()``) and ``clocks`` (NVML samples while the workload's launches run).
+
+``--impl reference`` times the CPU restatement of the reference's arithmetic (the reference's own oracle is a GPU
+library call and it has no CPU path) with all host threads on the same configurations.
 """
 from __future__ import annotations
 
@@ -46,9 +53,8 @@ def measured_peaks() -> tuple[float, str]:
 
 # ----------------------------------------------------------------------------------------------- workloads
 def _util():
-    sys.path.insert(0, str(ROOT / "tests"))
-    import _util
-    return _util
+    from eval_test_b200 import hostviews
+    return hostviews
 
 
 class GemvWorkload:
@@ -60,23 +66,28 @@ class GemvWorkload:
     dtype = "e2m1 x ue4m3 scales, block-scaled tensor-core products, fp32 accumulate, fp16 out"
     bound, kernel, scaling = "hbm", "gemv_tc_kernel", "weak"
 
-    def __init__(self, m=16384, k=16384, l=4):
-        self.m, self.k, self.l = m, k, l
+    def __init__(self, m=16384, k=16384, l=4, strong=False):
+        self.m, self.k, self.l, self.strong = m, k, l, strong
+        if strong:   # the same 16384 rows split M/N ways instead of 16384 rows per rank
+            self.name, self.scaling = f"gemv_m{m}_k{k}_l{l}_rowsplit", "strong"
 
     def small(self):
-        return GemvWorkload(m=4096, k=self.k, l=self.l)
+        return GemvWorkload(m=4096, k=self.k, l=self.l, strong=self.strong)
+
+    def _rows(self, world):
+        return self.m // world if self.strong else self.m
 
     def work(self, world=1, m=None) -> int:
         """Algorithmic bytes per rank and step: A + its scales + the vector and its scales + the fp16 output."""
-        m = self.m if m is None else m
+        m = self._rows(world) if m is None else m
         return self.l * (m * self.k // 2 + m * self.k // 16 + (self.k // 2 + self.k // 16) + 2 * m)
 
     def job(self, world=1) -> int:
-        return self.work() * world
+        return self.work(world) * world
 
     def make(self, rank, world, device):
         from eval_test_b200 import inputs
-        return inputs.gemv_quantized(self.m, self.k, self.l, seed=rank, device=device)
+        return inputs.gemv_quantized(self._rows(world), self.k, self.l, seed=rank, device=device)
 
     def run(self, data):
         from eval_test_b200 import nvfp4_gemv
@@ -91,25 +102,29 @@ class GemvWorkload:
         return (moved[0], moved[1], sfa, sfb, moved[2], moved[3], c)
 
     def config(self, world):
-        return {"workload": self.name, "m_per_gpu": self.m, "k": self.k, "l": self.l, "global_m": self.m * world,
+        rows = self._rows(world)
+        mb = self.work(world) / 1e6
+        return {"workload": self.name, "m_per_gpu": rows, "k": self.k, "l": self.l, "global_m": rows * world,
                 "sharding": "rows of A per rank, no collective",
-                "l2": f"inputs ({self.work() / 1e6:.0f} MB per step) larger than L2 (126 MB)",
+                "l2": (f"inputs ({mb:.0f} MB per step) larger than L2 (126 MB)" if mb > 132 else
+                       f"inputs ({mb:.0f} MB per step) fit in L2 at this split: 512 MiB written between steps"),
                 "generator": "N(0,1) seed = rank -> block-16 quantiser (scale = amax/6 as e4m3, RNE e2m1)"}
 
-    def cpu_sample(self, data, rows=2048):
-        u = _util()
-        rows = min(rows, self.m)
-        a, b, _, _, sfa_p, sfb_p, _ = data
-        args = (u.operand_np(a[:rows]), u.operand_np(b), u.scales_np(sfa_p[:, :, : rows // 128]), u.scales_np(sfb_p))
-        return args, self.work(m=rows), f"rows 0..{rows - 1} of each of the {self.l} batches, K = {self.k}"
+    def flush_l2(self, world):
+        return self.work(world) < 132e6
 
-    def cpu_data(self, rows=2048):
-        from eval_test_b200 import inputs
-        return inputs.gemv_quantized(min(rows, self.m), self.k, self.l, seed=0, device="cpu")
-
-    def cpu_run(self, args):
+    def cpu_samples(self, data):
+        """(route, callable, units, description) per CPU route; see cpu_baseline()."""
         from oracle import nvfp4_oracle as O
-        return O.c_gemv(*args)
+        u = _util()
+        a, b, _, _, sfa_p, sfb_p, _ = data
+        out = []
+        for route, rows, fn in (("fused_c", 8192, O.c_gemv), ("dequant_matmul", 2048, O.dq_gemv)):
+            rows = min(rows, a.shape[0]) // 128 * 128
+            args = (u.operand_np(a[:rows]), u.operand_np(b), u.scales_np(sfa_p[:, :, : rows // 128]), u.scales_np(sfb_p))
+            out.append((route, (lambda fn=fn, args=args: fn(*args)), self.work(m=rows),
+                        f"rows 0..{rows - 1} of each of the {self.l} batches, K = {self.k}"))
+        return out
 
 
 class GemmWorkload:
@@ -161,21 +176,22 @@ class GemmWorkload:
                 "l2": "operands + output (210 MB at 1 GPU) larger than L2 (126 MB)",
                 "generator": "N(0,1) seeded -> block-16 quantiser"}
 
-    def cpu_sample(self, data, rows=128, cols=1024):
+    def flush_l2(self, world):
+        return False
+
+    def cpu_samples(self, data):
+        from oracle import nvfp4_oracle as O
         u = _util()
         a, b, _, _, sfa_p, sfb_p, _ = data
-        cols = min(cols, b.shape[0])
-        args = (u.operand_np(a[:rows]), u.operand_np(b[:cols]), u.scales_np(sfa_p[:, :, : rows // 128]),
-                u.scales_np(sfb_p[:, :, : cols // 128]), self.alpha)
-        return args, self.work(m=rows, n=cols), f"rows 0..{rows - 1} of A against rows 0..{cols - 1} of B, K = {self.k}"
-
-    def cpu_data(self, rows=128, cols=1024):
-        from eval_test_b200 import inputs
-        return inputs.gemm_quantized(rows, cols, self.k, 1, seed=0, device="cpu")
-
-    def cpu_run(self, args):
-        from oracle import nvfp4_oracle as O
-        return O.c_gemm(*args)
+        out = []
+        for route, rows, cols, fn in (("fused_c", 128, 1024, O.c_gemm), ("dequant_matmul", a.shape[0], b.shape[0], O.dq_gemm)):
+            rows, cols = min(rows, a.shape[0]), min(cols, b.shape[0])
+            args = (u.operand_np(a[:rows]), u.operand_np(b[:cols]), u.scales_np(sfa_p[:, :, : (rows + 127) // 128]),
+                    u.scales_np(sfb_p[:, :, : cols // 128]), self.alpha)
+            what = ("the whole problem" if (rows, cols) == (a.shape[0], b.shape[0]) else
+                    f"rows 0..{rows - 1} of A against rows 0..{cols - 1} of B, K = {self.k}")
+            out.append((route, (lambda fn=fn, args=args: fn(*args)), self.work(m=rows, n=cols), what))
+        return out
 
 
 class GemmGatherWorkload(GemmWorkload):
@@ -275,22 +291,22 @@ class DualGemmWorkload(GemmWorkload):
         cfg["l2"] = "operands + output (193 MB at 1 GPU) larger than L2 (126 MB)"
         return cfg
 
-    def cpu_sample(self, data, rows=128, cols=512):
+    def cpu_samples(self, data):
+        from oracle import nvfp4_oracle as O
         u = _util()
         a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, _ = data
-        cols = min(cols, b1.shape[0])
-        nb = cols // 128
-        args = (u.operand_np(a[:rows]), u.operand_np(b1[:cols]), u.operand_np(b2[:cols]),
-                u.scales_np(sfa_p[:, :, : rows // 128]), u.scales_np(sfb1_p[:, :, :nb]), u.scales_np(sfb2_p[:, :, :nb]))
-        return args, self.work(m=rows, n=cols), f"rows 0..{rows - 1} of A against rows 0..{cols - 1} of B1, B2"
-
-    def cpu_data(self, rows=128, cols=512):
-        from eval_test_b200 import inputs
-        return inputs.dual_gemm_quantized(rows, cols, self.k, 1, seed=0, device="cpu")
-
-    def cpu_run(self, args):
-        from oracle import nvfp4_oracle as O
-        return O.c_dual_gemm(*args)
+        out = []
+        for route, rows, cols, fn in (("fused_c", 128, 512, O.c_dual_gemm),
+                                      ("dequant_matmul", a.shape[0], b1.shape[0], O.dq_dual_gemm)):
+            rows, cols = min(rows, a.shape[0]), min(cols, b1.shape[0])
+            nb = cols // 128
+            args = (u.operand_np(a[:rows]), u.operand_np(b1[:cols]), u.operand_np(b2[:cols]),
+                    u.scales_np(sfa_p[:, :, : (rows + 127) // 128]), u.scales_np(sfb1_p[:, :, :nb]),
+                    u.scales_np(sfb2_p[:, :, :nb]))
+            what = ("the whole problem" if (rows, cols) == (a.shape[0], b1.shape[0]) else
+                    f"rows 0..{rows - 1} of A against rows 0..{cols - 1} of B1, B2")
+            out.append((route, (lambda fn=fn, args=args: fn(*args)), self.work(m=rows, n=cols), what))
+        return out
 
 class DualGemmNvfp4Workload(DualGemmWorkload):
     """The same up-projection with the result emitted as NVFP4 (packed e2m1 + swizzled block scales) for the
@@ -323,16 +339,26 @@ class GroupedGemmWorkload:
     dtype = "e2m1 x ue4m3 scales on tcgen05 (kind::mxf4nvf4), fp32 accumulate, fp16 out"
     bound, kernel, scaling = "hbm", "gemm_kernel", "strong"
 
-    def __init__(self, g=64, n=4096, k=7168, mean=128.0):
+    def __init__(self, g=64, n=4096, k=7168, mean=128.0, forced_empty=()):
         from eval_test_b200 import inputs
         self.g, self.n, self.k = g, n, k
         self.ms = inputs.poisson_group_sizes(g, mean, 0, 1024, seed=0)
+        self.forced_empty = tuple(i for i in forced_empty if i < g)
+        for i in self.forced_empty:   # a seeded Poisson(128) draw never gives an empty group: force some
+            self.ms[i] = 0
+        if self.forced_empty:
+            self.name += f"_{len(self.forced_empty)}empty"
 
     def small(self):
-        return GroupedGemmWorkload(g=16)
+        return GroupedGemmWorkload(g=16, forced_empty=self.forced_empty)
+
+    def flush_l2(self, world):
+        return self.work(world) < 132e6
 
     def _mine(self, rank, world):
-        return self.ms[rank::world]
+        """Sizes of the groups of `rank`: whole groups, balanced by weight bytes (shard.assign_groups)."""
+        from eval_test_b200 import shard
+        return [self.ms[i] for i in shard.assign_groups(self.ms, world)[rank]]
 
     def _bytes(self, ms, n=None):
         n, k = (self.n if n is None else n), self.k
@@ -343,6 +369,9 @@ class GroupedGemmWorkload:
         """Algorithmic bytes of the busiest rank: weights and their scales of every non-empty group, activations,
         their (128-row padded) scales and the fp16 outputs."""
         return max(self._bytes(self._mine(r, world)) for r in range(world))
+
+    def flops(self) -> int:
+        return sum(2 * m * self.n * self.k for m in self.ms)
 
     def job(self, world=1) -> int:
         return self._bytes(self.ms)
@@ -376,28 +405,27 @@ class GroupedGemmWorkload:
         return {"workload": self.name, "groups": self.g, "n": self.n, "k": self.k, "sum_m": sum(self.ms),
                 "min_m": min(self.ms), "max_m": max(self.ms), "empty_groups": sum(m == 0 for m in self.ms),
                 "flop_per_step": sum(2 * m * self.n * self.k for m in self.ms),
-                "sharding": "groups dealt round-robin to ranks, no collective",
-                "l2": f"weights ({self.work() / 1e6:.0f} MB per step) larger than L2 (126 MB)",
+                "forced_empty": list(self.forced_empty),
+                "sharding": "whole groups per rank, balanced by weight bytes (non-empty groups), no collective",
+                "l2": (f"weights ({self.work(world) / 1e6:.0f} MB per step and rank) larger than L2 (126 MB)"
+                       if self.work(world) > 132e6 else
+                       f"{self.work(world) / 1e6:.0f} MB per step and rank fit in L2: 512 MiB written between steps"),
                 "generator": "M_g = clip(Poisson(128), 0, 1024), numpy default_rng(0); operands N(0,1) -> quantiser"}
 
-    def cpu_sample(self, data, groups=2, cols=256):
+    def cpu_samples(self, data):
+        from oracle import nvfp4_oracle as O
         u = _util()
         abc, _, sfs_p, _ = data
-        args = []
-        for (a, b, _), (sa, sb) in list(zip(abc, sfs_p))[:groups]:
-            args.append((u.operand_np(a)[0], u.operand_np(b[:cols])[0], u.scales_np(sa),
-                         u.scales_np(sb[:, :, : cols // 128])))
-        ms = [a[0].shape[0] for a in args]
-        return args, self._bytes(ms, n=cols), f"groups 0..{groups - 1}, rows 0..{cols - 1} of each B, K = {self.k}"
-
-    def cpu_data(self, groups=2, cols=256):
-        from eval_test_b200 import inputs
-        ms = self.ms[:groups]
-        return inputs.grouped_gemm_quantized(ms, [cols] * groups, [self.k] * groups, groups, seed=0, device="cpu")
-
-    def cpu_run(self, args):
-        from oracle import nvfp4_oracle as O
-        return O.c_grouped_gemm(args)
+        live = [i for i, (a, _, _) in enumerate(abc) if a.shape[0] > 0]
+        out = []
+        for route, groups, cols, fn in (("fused_c", 2, 256, O.c_grouped_gemm), ("dequant_matmul", 8, self.n, O.dq_grouped_gemm)):
+            pick = live[:groups]
+            args = [(u.operand_np(abc[i][0])[0], u.operand_np(abc[i][1][:cols])[0], u.scales_np(sfs_p[i][0]),
+                     u.scales_np(sfs_p[i][1][:, :, : cols // 128])) for i in pick]
+            ms = [g[0].shape[0] for g in args]
+            what = f"the first {len(pick)} non-empty groups" + ("" if cols == self.n else f", rows 0..{cols - 1} of each B")
+            out.append((route, (lambda fn=fn, args=args: fn(args)), self._bytes(ms, n=cols), what + f", K = {self.k}"))
+        return out
 
 
 class QuantizeWorkload:
@@ -445,35 +473,44 @@ class QuantizeWorkload:
         return {"workload": self.name, "rows": self.rows, "k": self.k, "sharding": "one operand per rank",
                 "l2": "1 GiB input larger than L2 (126 MB)", "generator": "N(0,1), seed = rank"}
 
-    def cpu_sample(self, data, rows=1024):
-        x = data[0][:, :rows].cpu()
-        return (x,), self.work(rows=rows), f"rows 0..{rows - 1} (torch CPU ops, formats.quantize_nvfp4 + swizzle)"
+    def flush_l2(self, world):
+        return False
 
-    def cpu_data(self, rows=1024):
-        import torch
-        return [torch.randn((1, rows, self.k), generator=torch.Generator().manual_seed(0)), None]
-
-    def cpu_run(self, args):
+    def cpu_samples(self, data, rows=1024):
         from eval_test_b200 import formats as F
-        packed, sf = F.quantize_nvfp4(args[0])
-        return packed, F.swizzle_scales(sf)
+        x = data[0][:, :rows].cpu()
+
+        def run():
+            packed, sf = F.quantize_nvfp4(x)
+            return packed, F.swizzle_scales(sf)
+        return [("torch_ops", run, self.work(rows=rows),
+                 f"rows 0..{rows - 1} (torch CPU ops, formats.quantize_nvfp4 + swizzle)")]
 
 
-WORKLOADS = {"gemv": GemvWorkload, "gemm": GemmWorkload, "dual_gemm": DualGemmWorkload,
+FORCED_EMPTY = (3, 17, 18, 40, 63)
+WORKLOADS = {"gemv": GemvWorkload, "gemv_rowsplit": lambda: GemvWorkload(strong=True),
+             "grouped_gemm_empty": lambda: GroupedGemmWorkload(forced_empty=FORCED_EMPTY),
+             "gemm": GemmWorkload, "dual_gemm": DualGemmWorkload,
              "dual_gemm_nvfp4": DualGemmNvfp4Workload,
              "gemm_gather_fused": lambda: GemmGatherWorkload(True), "gemm_gather_nccl": lambda: GemmGatherWorkload(False),
              "grouped_gemm": GroupedGemmWorkload, "quantize": QuantizeWorkload}
 
 
+
+
 # ----------------------------------------------------------------------------------------------- clocks
 class ClockSampler:
-    """Polls NVML (SM clock, event reasons) for one GPU while the timed region runs."""
+    """Polls NVML (SM clock, power, event reasons) for one GPU while launches run.  The timed region of a short run
+    lasts a few milliseconds, less than one NVML refresh, so the record also covers an untimed continuation of the
+    same launches (see measure()): what the clock settles at under this workload, power cap included."""
     REASONS = {0x1: "gpu_idle", 0x2: "applications_clocks_setting", 0x4: "sw_power_cap", 0x8: "hw_slowdown",
                0x10: "sync_boost", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
                0x80: "hw_power_brake_slowdown", 0x100: "display_clock_setting"}
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.power, self.reasons, self.max_mhz = [], [], set(), None
+        self.in_timed = 0
+        self.timed = False
         self._stop = threading.Event()
         self._thr = None
         try:
@@ -490,13 +527,15 @@ class ClockSampler:
         while not self._stop.is_set():
             try:
                 self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self.h) / 1000.0)
+                self.in_timed += 1 if self.timed else 0
                 bits = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.h))
                 for bit, name in self.REASONS.items():
                     if bits & bit and name != "gpu_idle":
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(0.0005)
+            time.sleep(0.001)
 
     def __enter__(self):
         if self.nv is not None:
@@ -510,64 +549,131 @@ class ClockSampler:
             self._thr.join()
 
     def summary(self):
-        s = sorted(self.samples)
-        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
-                "samples": len(s), "reasons": sorted(self.reasons)}
+        s, w = sorted(self.samples), sorted(self.power)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_min_mhz": s[0] if s else None, "sm_max_mhz": self.max_mhz,
+                "power_w": w[len(w) // 2] if w else None, "samples": len(s), "samples_in_timed_region": self.in_timed,
+                "reasons": sorted(self.reasons),
+                "window": "the timed region and an untimed continuation of the same launches (at least 0.25 s)"}
 
 
 # ----------------------------------------------------------------------------------------------- CPU arm
-def _time_cpu(wl, args, budget_s=20.0):
+def _host_threads() -> int:
+    """All host cores, set explicitly: a launcher may have exported OMP_NUM_THREADS=1 for its workers."""
+    import torch
+    from oracle import nvfp4_oracle as O
+    n = os.cpu_count() or 1
+    O.set_num_threads(n)
+    torch.set_num_threads(n)
+    return n
+
+
+def _time_cpu(fn, budget_s=8.0, max_runs=10):
+    """One warm-up run (thread pools, page faults), then up to `max_runs` timed runs within the budget.  Returns the
+    per-run seconds and, for routes that report them, the (dequantise, matmul) phase times."""
     t0 = time.perf_counter()
-    wl.cpu_run(args)
-    best = time.perf_counter() - t0
-    for _ in range(2):
-        if best * 3 > budget_s:
-            break
+    fn()
+    first = time.perf_counter() - t0
+    runs, phases = [], []
+    spent = first
+    while len(runs) < max_runs and (not runs or spent + first <= budget_s):
         t0 = time.perf_counter()
-        wl.cpu_run(args)
-        best = min(best, time.perf_counter() - t0)
-    return best
+        res = fn()
+        dt = time.perf_counter() - t0
+        runs.append(dt)
+        spent += dt
+        if isinstance(res, tuple) and len(res) == 3 and isinstance(res[1], float):
+            phases.append((res[1], res[2]))
+    return runs, phases
+
+
+def _median(xs):
+    xs = sorted(xs)
+    return xs[len(xs) // 2]
 
 
 def cpu_baseline(wl, data):
-    """The CPU oracle on the host cores over a bounded sample of the same inputs (best of 3)."""
+    """The CPU restatement of the path on the host cores (all of them), two routes, median of up to 10 runs each:
+    `fused_c`: the C oracle (exact integer block dot products, fp32 accumulation, OpenMP) on a bounded row sample;
+    `dequant_matmul`: dequantise to fp32 (C, OpenMP) then torch.matmul in fp32 - the shape of computation the
+    reference's oracle has - on the whole problem where that takes seconds, else on a sample; its two phases are
+    listed apart.  `value` is the faster route's."""
     from oracle import nvfp4_oracle as O
     O.build()
-    args, units, what = wl.cpu_sample(data)
-    best = _time_cpu(wl, args)
-    return {"value": units / best / wl.per, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
-            "sample": what + "; best of 3", "seconds": best}
+    cores = _host_threads()
+    routes = {}
+    for route, fn, units, what in wl.cpu_samples(data):
+        runs, phases = _time_cpu(fn)
+        med = _median(runs)
+        rec = {"value": units / med / wl.per, "seconds": med, "runs": len(runs), "spread": (max(runs) - min(runs)) / med,
+               "sample": what}
+        if phases:
+            rec["dequantise_s"] = _median([p[0] for p in phases])
+            rec["matmul_s"] = _median([p[1] for p in phases])
+        routes[route] = rec
+    best = max(routes, key=lambda r: routes[r]["value"])
+    return {"value": routes[best]["value"], "unit": wl.unit, "cores": cores, "kind": "port", "route": best,
+            "sample": routes[best]["sample"] + f"; median of {routes[best]['runs']} runs after a warm-up run",
+            "routes": routes}
 
 
-def run_reference(args, wl):
-    """Reference arm: the reference has no CPU implementation of this path (its oracle is a cuBLASLt call), so
-    this times the CPU restatement of it with all host threads; each step is a bounded sample (rank 0 only)."""
-    if int(os.environ.get("RANK", "0")) != 0:
-        return
+def cpu_c0():
+    """BASELINE configuration 0, the CPU-runnable case, in full: GEMM 128 x 256 x 512, N(0,1) seed 0 through the
+    quantiser, alpha = 1, both CPU routes."""
+    from eval_test_b200 import inputs
+    wl = GemmWorkload(128, 256, 512)
+    wl.alpha = 1.0
+    rec = cpu_baseline(wl, inputs.gemm_quantized(128, 256, 512, 1, seed=0, device="cpu"))
+    rec["config"] = {"workload": "gemm_m128_n256_k512", "flop": wl.work()}
+    return rec
+
+
+def _reference_record(wl, args, steps, warmup):
+    """K steps of the faster CPU route on this workload's sample (see cpu_baseline)."""
+    import torch
     from oracle import nvfp4_oracle as O
     O.build()
-    data = wl.cpu_data()
-    sample, units, what = wl.cpu_sample(data)
-    for _ in range(max(1, min(args.warmup, 2))):
-        wl.cpu_run(sample)
+    cores = _host_threads()
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if torch.cuda.is_available() else "cpu"
+    data = wl.make(0, 1, dev)     # the same seeded inputs as the GPU arm's rank 0; generated where it is fastest
+    probes = []
+    for route, fn, units, what in wl.cpu_samples(data):
+        t0 = time.perf_counter()
+        fn()
+        probes.append((units / (time.perf_counter() - t0), route, fn, units, what))
+    del data
+    _, route, fn, units, what = max(probes, key=lambda p: p[0])
+    for _ in range(max(0, min(warmup, 2) - 1)):
+        fn()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
-        wl.cpu_run(sample)
-    dt = (time.perf_counter() - t0) / args.steps
+    for _ in range(steps):
+        fn()
+    dt = (time.perf_counter() - t0) / steps
     val = units / dt / wl.per
-    line = {"impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": args.gpus,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+    return {"impl": "reference", "metric": wl.metric, "value": val, "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
             "scaling": wl.scaling, "vs_baseline": None,
-            "dtype": getattr(wl, "cpu_dtype", "e2m1 x ue4m3 scales, exact int32 block dots, fp32 accumulate, fp16 out (CPU)"),
-            "data": "synthetic",
-            "config": wl.config(args.gpus),
-            "cpu_baseline": {"value": val, "unit": wl.unit, "cores": O.num_threads(), "kind": "port",
+            "dtype": getattr(wl, "cpu_dtype", "e2m1 x ue4m3 scales, fp32 accumulate, fp16 out (CPU, " + route + ")"),
+            "data": "synthetic", "config": wl.config(args.gpus),
+            "cpu_baseline": {"value": val, "unit": wl.unit, "cores": cores, "kind": "port", "route": route,
                              "sample": "each step = " + what},
             "e2e": {"value": val, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+
+
+def run_reference(args, names):
+    """Reference arm: the reference has no CPU implementation of this path (its oracle is a cuBLASLt call), so this
+    times the CPU restatement of it with all host threads, rank 0 only; the other ranks exit without work."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    head = _reference_record(WORKLOADS[names[0]](), args, args.steps, args.warmup)
+    if len(names) > 1:
+        head["workloads"] = {n: _reference_record(WORKLOADS[n](), args, max(1, min(args.steps, 5)), 1) for n in names[1:]}
+    print(json.dumps(head), flush=True)
 
 
 # ----------------------------------------------------------------------------------------------- GPU arm
+NOMINAL = {"hbm": 8000.0, "tensor": 9000.0}   # GB/s and TFLOP/s the target statement quotes
+
+
 def tensor_peak_tflops() -> tuple[float, str]:
     """Dense FP4 ceiling used for tensor-bound workloads: 4 x the measured bf16 GEMM rate of this pool (the
     FP4 tensor path issues 4 x the bf16 flops per clock: 9 vs 2.25 PFLOP/s nominal)."""
@@ -580,68 +686,90 @@ def tensor_peak_tflops() -> tuple[float, str]:
     return 4.0 * 1590.0, "4 x fallback bf16"
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=500)
-    ap.add_argument("--warmup", type=int, default=10)
-    ap.add_argument("--workload", default="gemv", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=5)
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--small", action="store_true", help="shrink the workload (profiler captures); not a bench value")
-    args = ap.parse_args()
-    wl = WORKLOADS[args.workload]()
-    if args.small:
-        wl = wl.small()
+class Ctx:
+    def __init__(self, args):
+        import torch
+        import torch.distributed as dist
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        assert self.world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={self.world}"
+        torch.cuda.set_device(self.local_rank)
+        self.dev = torch.device("cuda", self.local_rank)
+        self.dist = dist
+        if self.world > 1:
+            dist.init_process_group("nccl", device_id=self.dev)
+        self.flush_buf = None
 
-    if args.impl == "reference":
-        run_reference(args, wl)
-        return
-
-    import torch
-    import torch.distributed as dist
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    assert args.warmup >= 3 or args.small, "at least 3 warm-up steps"
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-
-    from eval_test_b200 import _lib
-    _lib.load()
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
+    def barrier(self):
+        import torch
+        if self.world > 1:
+            self.dist.barrier()
         torch.cuda.synchronize()
 
+    def flush(self):
+        """Write 512 MiB (four times the L2) on the current stream."""
+        import torch
+        if self.flush_buf is None:
+            self.flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=self.dev)
+        self.flush_buf.fill_(0)
+
+    def close(self):
+        if self.world > 1:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def measure(wl, ctx, args, with_cpu=True):
+    """All ranks run; rank 0 returns the record."""
+    import torch
+    from eval_test_b200 import _lib
+    rank, world, dev = ctx.rank, ctx.world, ctx.dev
     data = wl.make(rank, world, dev)
     stream = torch.cuda.current_stream()
+    flush = hasattr(wl, "flush_l2") and wl.flush_l2(world)
 
     for _ in range(args.warmup):
         wl.run(data)
-    barrier()
+    ctx.barrier()
 
-    # ---- timed region: K steps, device-resident inputs ----
-    # One kernel launch per step and nothing else on the stream, so the average launch duration is the event time
-    # over the region divided by the launches (launch gaps included: an upper bound of the kernel's own time; an
-    # event pair around every launch would put two more stream operations between the kernels).
-    t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        t_begin.record(stream)
-        for _ in range(args.steps):
-            wl.run(data)
-        t_end.record(stream)
-        barrier()
-    total_ms = t_begin.elapsed_time(t_end)
+    with ClockSampler(ctx.local_rank) as clocks:
+        if not flush:
+            # ---- timed region: K steps back to back, device-resident inputs larger than the L2 ----
+            # One kernel launch per step and nothing else on the stream, so the average launch duration is the event
+            # time over the region divided by the launches (launch gaps included: an upper bound of the kernel's own
+            # time; an event pair around every launch would put two more stream operations between the kernels).
+            t_begin, t_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ctx.barrier()
+            clocks.timed = True
+            t_begin.record(stream)
+            for _ in range(args.steps):
+                wl.run(data)
+            t_end.record(stream)
+            ctx.barrier()
+            clocks.timed = False
+            total_ms = t_begin.elapsed_time(t_end)
+        else:
+            # ---- this rank's inputs fit in the L2: 512 MiB are written before every step, outside its event pair ----
+            pairs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(args.steps)]
+            ctx.barrier()
+            clocks.timed = True
+            for b, e in pairs:
+                ctx.flush()
+                b.record(stream)
+                wl.run(data)
+                e.record(stream)
+            ctx.barrier()
+            clocks.timed = False
+            total_ms = sum(b.elapsed_time(e) for b, e in pairs)
+        # ---- untimed continuation of the same launches, so that NVML sees the clock this workload settles at ----
+        t0 = time.perf_counter()
+        while time.perf_counter() - t0 < 0.25:
+            for _ in range(20):
+                wl.run(data)
+            torch.cuda.synchronize()
     kern_ms = total_ms / args.steps
-    status = _lib.device_status(local_rank)
+    status = _lib.device_status(ctx.local_rank)
     assert status == 0, f"device status {status}: {_lib.strerror(status)}"
 
     # ---- end to end: pinned host inputs -> device, kernel, outputs -> host, every step ----
@@ -673,21 +801,22 @@ def main():
     e2e_steps = 1 if args.small else args.e2e_steps
     for _ in range(0 if args.small else 2):
         e2e_step()
-    barrier()
+    ctx.barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record(stream)
     for _ in range(e2e_steps):
         e2e_step()
     e1.record(stream)
-    barrier()
+    ctx.barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps
 
     # ---- max over ranks ----
     t = torch.tensor([total_ms, kern_ms, e2e_ms], device=dev, dtype=torch.float64)
     if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ctx.dist.all_reduce(t, op=ctx.dist.ReduceOp.MAX)
     total_ms, kern_ms, e2e_ms = (float(v) for v in t.tolist())
 
+    line = None
     if rank == 0:
         if wl.bound == "hbm":
             peak, peak_kind = measured_peaks()
@@ -706,13 +835,16 @@ def main():
             "data": "synthetic", "config": wl.config(world),
             "roofline": {"bound": wl.bound, "kernel": wl.kernel, "achieved": achieved, "peak": peak,
                          "peak_kind": peak_kind if wl.bound == "tensor" else f"of {peak_kind}", "unit": peak_unit,
-                         "frac": achieved / peak, "units_per_launch": units, "us_per_launch": kern_ms * 1e3,
+                         "frac": achieved / peak, "frac_of_nominal": achieved / NOMINAL[wl.bound],
+                         "nominal": NOMINAL[wl.bound], "units_per_launch": units, "us_per_launch": kern_ms * 1e3,
                          "traffic": None},
             "e2e": {"value": job / (e2e_ms * 1e-3) / wl.per, "unit": wl.unit,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms,
                     "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks.summary(),
         }
+        if hasattr(wl, "flops"):            # an HBM-bound GEMM: the flop rate beside the byte rate
+            line["tflops"] = wl.flops() / (ms_per_step * 1e-3) / 1e12
         if hasattr(wl, "target_us"):   # compute + collective: achieved time against the slower of the two floors
             tgt = wl.target_us(world, peak)
             line["roofline"].update({"bound": "tensor or nvlink", "target_us": tgt, "frac": tgt / (kern_ms * 1e3),
@@ -723,13 +855,54 @@ def main():
                 line["roofline"]["traffic"] = json.loads(traffic.read_text()).get(wl.name)
             except Exception:
                 pass
-        if world == 1 and not args.no_cpu_baseline and not args.small:
+        if world == 1 and with_cpu and not args.no_cpu_baseline and not args.small:
             line["cpu_baseline"] = cpu_baseline(wl, data)
-        print(json.dumps(line), flush=True)
+    del data, e2e_data, dev_in, host_in, host_out, ins, outs
+    torch.cuda.empty_cache()
+    return line
 
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+
+DEFAULT_SET = ("gemv", "gemm", "dual_gemm", "grouped_gemm", "grouped_gemm_empty")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=500)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--workload", default="all", choices=["all"] + sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=5)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--small", action="store_true", help="shrink the workload (profiler captures); not a bench value")
+    args = ap.parse_args()
+    names = list(DEFAULT_SET) + (["gemv_rowsplit"] if args.gpus > 1 else []) if args.workload == "all" else [args.workload]
+
+    if args.impl == "reference":
+        run_reference(args, names)
+        return
+
+    assert args.warmup >= 3 or args.small, "at least 3 warm-up steps"
+    ctx = Ctx(args)
+    from eval_test_b200 import _lib
+    _lib.load()
+
+    def wl_of(name):
+        wl = WORKLOADS[name]()
+        return wl.small() if args.small else wl
+
+    head = measure(wl_of(names[0]), ctx, args)
+    subs = {}
+    for name in names[1:]:
+        subs[name] = measure(wl_of(name), ctx, args)
+    if ctx.rank == 0:
+        if subs:
+            head["workloads"] = subs
+            head["gpu_launches_all_workloads"] = args.steps * len(names)
+            if ctx.world == 1 and not args.no_cpu_baseline and not args.small:
+                head["cpu_baseline_c0"] = cpu_c0()
+        print(json.dumps(head), flush=True)
+    ctx.close()
 
 
 if __name__ == "__main__":

@@ -8,10 +8,14 @@
 //
 // Roles are those of the single-CTA kernel (warp 0 producer, warp 1 MMA, warps 2..5 epilogue) with these changes:
 //   * both CTAs run a producer for their own tiles with plain TMA loads (no multicast: each CTA fetches what it
-//     keeps; the scales of B are needed by both CTAs and are fetched by both);
-//   * only the leader CTA (cluster rank 0) issues tcgen05.cp / tcgen05.mma (.cta_group::2); it waits for its own
-//     "full" barrier and for a "peer full" barrier on which warp 1 of the peer CTA arrives (over the cluster)
-//     once the peer's stage has landed;
+//     keeps; the scales of B are needed by both CTAs and are fetched by both).  Every load of either CTA counts its
+//     bytes on the LEADER's "full" barrier of the stage (cp.async.bulk.tensor ... .cta_group::2 lets the barrier
+//     live in the other CTA of the pair), so one barrier says "both halves have landed" and no thread relays
+//     anything.  (A relay by a remote mbarrier.arrive.release.cluster per stage was measured at about 850 cycles
+//     per K step, serialised in the relaying thread: the pair ran at 1 350 cycles per K step instead of 512.)
+//     The scale atoms therefore come through 2-D tensor maps over the scale buffers (rows of 512 bytes) instead
+//     of 1-D bulk copies, which cannot signal a barrier in another CTA;
+//   * only the leader CTA (cluster rank 0) issues tcgen05.cp / tcgen05.mma (.cta_group::2);
 //   * tcgen05.commit signals the barrier at the same shared-memory offset in both CTAs, which frees the stage for
 //     both producers / publishes the accumulator to both epilogues;
 //   * both CTAs' epilogue warps drain their own 128 accumulator rows and arrive on the LEADER's "drained" barriers.
@@ -43,7 +47,9 @@ constexpr size_t PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
 template <bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                 const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmap_b2, const __grid_constant__ CUtensorMap tmap_sfa,
+                 const __grid_constant__ CUtensorMap tmap_sfb, const __grid_constant__ CUtensorMap tmap_sfb2,
+                 const GemmParams p) {
     constexpr int BN = DUAL ? 128 : 256;                 // output columns of the pair tile
     constexpr uint32_t SF_COLS = 16 + 32;                // TMEM columns of one stage's scales (A 16, B 32)
     constexpr uint32_t SF_BASE = TMEM_COLS - 2 * SF_COLS;
@@ -54,23 +60,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 
     extern __shared__ uint8_t smem_raw[];
     // same layout in both CTAs (remote arrivals and pair-wide commits address barriers by offset)
-    __shared__ __align__(8) uint64_t bars[3 * STAGES + 5];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
     __shared__ uint32_t tmem_base_slot;
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();             // 0 = leader
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
-    const uint32_t peer_full0 = smem_u32(&bars[2 * STAGES]);          // leader's copy is the one used
-    const uint32_t acc_full0 = smem_u32(&bars[3 * STAGES]);           // [2], signalled in both CTAs
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]);           // [2], signalled in both CTAs
     const uint32_t acc_empty0 = acc_full0 + 16;                       // [2], leader's copy used, 8 arrivals
     const uint32_t ovl_free = acc_full0 + 32;                         // leader's copy used, 8 arrivals
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) {
-            mbar_init(full0 + 8 * s, 1);
+            mbar_init(full0 + 8 * s, 1);      // the leader's copy is the one used: one arrival + both CTAs' bytes
             mbar_init(empty0 + 8 * s, 1);
-            mbar_init(peer_full0 + 8 * s, 1);
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(acc_full0 + 8 * b, 1);
@@ -80,7 +84,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         fence_mbar_init();
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
-        if (DUAL) prefetch_tmap(&tmap_b2);
+        prefetch_tmap(&tmap_sfa);
+        prefetch_tmap(&tmap_sfb);
+        if (DUAL) {
+            prefetch_tmap(&tmap_b2);
+            prefetch_tmap(&tmap_sfb2);
+        }
     }
     if (warp == 1) {
         tmem_alloc_pair(smem_u32(&tmem_base_slot), TMEM_COLS);
@@ -97,78 +106,66 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int kiters = p.K / BK;
     const int RA = (p.M + 127) / 128, RB = p.N / 128;
-    const size_t sf_row_block = (size_t)(p.K / 64) * 512;
+    const int atoms_per_block = p.K / 64;                // scale atoms (512 bytes) of one 128-row block
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer (both CTAs, own tiles)
         if (elect_one()) {
             uint32_t it = 0;
             bool alive = true;
+            const uint32_t leader_full0 = mapa_shared(full0, 0);
             for (int t = pair; alive && t < total_tiles; t += npairs) {
                 const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
                 const int m0 = tc.mt * 256 + (int)rank * 128;     // this CTA's A rows
                 const int n0 = tc.nt * BN;
                 const bool a_rows_exist = m0 < p.M;
-                const uint8_t* sfa_t = p.sfa + ((size_t)tc.l * RA + (m0 >> 7)) * sf_row_block;
-                const size_t blk = (size_t)tc.l * RB + n0 / 128;
+                const bool peer_rows_exist = tc.mt * 256 + 128 < p.M;
+                const int atom_a = (tc.l * RA + (m0 >> 7)) * atoms_per_block;
+                const int atom_b = (tc.l * RB + n0 / 128) * atoms_per_block;
                 for (int kit = 0; kit < kiters; kit++, it++) {
                     const int slot = it % STAGES;
-                    if (!mbar_wait(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns)) {
+                    if (!mbar_wait_cluster(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns)) {
                         report_status(p.status, DEV_TIMEOUT_PRODUCER);
                         alive = false;
                         break;
                     }
-                    const uint32_t full = full0 + 8 * slot;
+                    const uint32_t full = leader_full0 + 8 * slot;
                     const uint32_t sA = smem0 + slot * PAIR_STAGE_BYTES;
                     const uint32_t sB = sA + PAIR_A_BYTES;
                     const uint32_t sSFA = sB + PAIR_B_BYTES;
                     const uint32_t sSFB = sSFA + PAIR_SFA_BYTES;
                     const int k0 = kit * BK;
-                    // rows of A beyond M (second CTA of the last row tile) read as zeros; their scale block
-                    // does not exist and is not fetched
-                    mbar_arrive_expect_tx(full, PAIR_A_BYTES + PAIR_B_BYTES + PAIR_SFB_BYTES +
-                                                    (a_rows_exist ? PAIR_SFA_BYTES : 0u));
-                    tma_load_3d(sA, &tmap_a, k0, m0, tc.l, full);
-                    const size_t koff = (size_t)(k0 / 64) * 512;
-                    if (a_rows_exist) bulk_g2s(sSFA, sfa_t + koff, 2048u, full);
+                    const int kx = k0 >> p.kshift;
+                    const int ka = k0 / 64;
+                    // the leader announces the bytes of BOTH CTAs.  Rows of A beyond M (second CTA of the last row
+                    // tile) read as zeros; their scale block does not exist and is not fetched
+                    if (rank == 0)
+                        mbar_arrive_expect_tx(full0 + 8 * slot, 2u * (PAIR_A_BYTES + PAIR_B_BYTES + PAIR_SFB_BYTES) +
+                                                                    PAIR_SFA_BYTES + (peer_rows_exist ? PAIR_SFA_BYTES : 0u));
+                    tma_load_3d_pair(sA, &tmap_a, kx, m0, tc.l, full);
+                    if (a_rows_exist) tma_load_2d_pair(sSFA, &tmap_sfa, 0, atom_a + ka, full);
                     if (DUAL) {
                         // leader keeps the B1 tile, peer the B2 tile; both need both scale blocks
-                        tma_load_3d(sB, rank == 0 ? &tmap_b : &tmap_b2, k0, n0, tc.l, full);
-                        bulk_g2s(sSFB, p.sfb + blk * sf_row_block + koff, 2048u, full);
-                        bulk_g2s(sSFB + 2048u, p.sfb2 + blk * sf_row_block + koff, 2048u, full);
+                        tma_load_3d_pair(sB, rank == 0 ? &tmap_b : &tmap_b2, kx, n0, tc.l, full);
+                        tma_load_2d_pair(sSFB, &tmap_sfb, 0, atom_b + ka, full);
+                        tma_load_2d_pair(sSFB + 2048u, &tmap_sfb2, 0, atom_b + ka, full);
                     } else {
-                        tma_load_3d(sB, &tmap_b, k0, n0 + (int)rank * 128, tc.l, full);
-                        bulk_g2s(sSFB, p.sfb + blk * sf_row_block + koff, 2048u, full);
-                        bulk_g2s(sSFB + 2048u, p.sfb + (blk + 1) * sf_row_block + koff, 2048u, full);
+                        tma_load_3d_pair(sB, &tmap_b, kx, n0 + (int)rank * 128, tc.l, full);
+                        tma_load_2d_pair(sSFB, &tmap_sfb, 0, atom_b + ka, full);
+                        tma_load_2d_pair(sSFB + 2048u, &tmap_sfb, 0, atom_b + atoms_per_block + ka, full);
                     }
                 }
             }
         }
     } else if (warp == 1) {
         if (elect_one()) {
-            if (rank != 0) {
-                // -------------------------------------------------------------- peer: relay "stage landed"
-                const uint32_t leader_peer_full0 = mapa_shared(peer_full0, 0);
-                uint32_t it = 0;
-                bool alive = true;
-                for (int t = pair; alive && t < total_tiles; t += npairs) {
-                    for (int kit = 0; kit < kiters; kit++, it++) {
-                        const int slot = it % STAGES;
-                        if (!mbar_wait(full0 + 8 * slot, (it / STAGES) & 1, p.budget_ns)) {
-                            report_status(p.status, DEV_TIMEOUT_CONSUMER);
-                            alive = false;
-                            break;
-                        }
-                        mbar_arrive_cluster(leader_peer_full0 + 8 * slot);
-                    }
-                }
-            } else {
+            if (rank == 0) {
                 // -------------------------------------------------------------- leader: MMA issuer for the pair
                 constexpr uint32_t idesc = make_idesc_nvfp4(256, 256);
                 uint32_t it = 0, tile_it = 0;
                 bool alive = true;
 #ifdef NVFP4_PROFILE
-                long long prof_acc = 0, prof_full = 0, prof_peer = 0;
+                long long prof_acc = 0, prof_full = 0;
                 const long long prof_begin = clock64();
 #endif
                 for (int t = pair; alive && t < total_tiles; t += npairs, tile_it++) {
@@ -192,13 +189,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         bool got;
                         {
                             PROF_T0();
-                            got = mbar_wait(full0 + 8 * slot, par, p.budget_ns);
+                            got = mbar_wait_cluster(full0 + 8 * slot, par, p.budget_ns);   // both CTAs' bytes
                             PROF_ADD(prof_full);
-                        }
-                        if (got) {
-                            PROF_T0();
-                            got = mbar_wait_cluster(peer_full0 + 8 * slot, par, p.budget_ns);
-                            PROF_ADD(prof_peer);
                         }
                         if (!got) {
                             report_status(p.status, DEV_TIMEOUT_CONSUMER);
@@ -228,10 +220,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 }
 #ifdef NVFP4_PROFILE
                 if (p.prof) {
-                    p.prof[3 * blockIdx.x + 0] = prof_acc;
-                    p.prof[3 * blockIdx.x + 1] = prof_full;
-                    p.prof[3 * blockIdx.x + 2] = clock64() - prof_begin;
-                    p.prof[3 * blockIdx.x + 3] = prof_peer;
+                    p.prof[8 * blockIdx.x + 0] = prof_acc;
+                    p.prof[8 * blockIdx.x + 1] = prof_full;
+                    p.prof[8 * blockIdx.x + 2] = clock64() - prof_begin;
+                    p.prof[8 * blockIdx.x + 6] = it;
                 }
 #endif
             }
@@ -334,7 +326,20 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<DUAL>, ta, tb, tb2, p);
+    GemmParams q = p;
+    q.kshift = operand_kshift();
+    const long ka = p.K / 64;
+    CUtensorMap tsa, tsb, tsb2;
+    rc = make_scale_tmap(&tsa, p.sfa, (long)p.L * ((p.M + 127) / 128) * ka);
+    if (rc) return rc;
+    rc = make_scale_tmap(&tsb, p.sfb, (long)p.L * (p.N / 128) * ka);
+    if (rc) return rc;
+    tsb2 = tsb;
+    if (DUAL) {
+        rc = make_scale_tmap(&tsb2, p.sfb2, (long)p.L * (p.N / 128) * ka);
+        if (rc) return rc;
+    }
+    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<DUAL>, ta, tb, tb2, tsa, tsb, tsb2, q);
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
 

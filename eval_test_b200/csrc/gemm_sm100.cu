@@ -64,6 +64,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 5];
     __shared__ uint32_t tmem_base_slot;
+#ifdef NVFP4_PROFILE
+    __shared__ long long prof_issue[STAGES];   // clock at which the producer issued a stage's loads
+#endif
 
     // operand tiles need 1024-byte alignment for the 128-byte swizzle
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -106,26 +109,39 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         if (elect_one()) {
             uint32_t it = 0;
             bool alive = true;
+#ifdef NVFP4_PROFILE
+            long long prof_empty = 0;
+#endif
             for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x) {
                 const TileInfo ti = locate<BN, DUAL, GROUPED>(t, p, &tmap_a, &tmap_b, &tmap_b2);
                 for (int kit = 0; kit < ti.kiters; kit++, it++) {
                     const int slot = it % STAGES;
-                    if (!mbar_wait(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns)) {
+                    bool free_;
+                    {
+                        PROF_T0();
+                        free_ = mbar_wait(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns);
+                        PROF_ADD(prof_empty);
+                    }
+                    if (!free_) {
                         report_status(p.status, DEV_TIMEOUT_PRODUCER);
                         alive = false;
                         break;
                     }
+#ifdef NVFP4_PROFILE
+                    prof_issue[slot] = clock64();
+#endif
                     const uint32_t full = full0 + 8 * slot;
                     const uint32_t sA = smem0 + slot * STAGE_BYTES;
                     const uint32_t sB = sA + A_BYTES;
                     const uint32_t sSFA = sB + B_BYTES;
                     const uint32_t sSFB = sSFA + SFA_BYTES;
                     const int k0 = kit * BK;
+                    const int kx = k0 >> p.kshift;
                     const uint32_t tx = A_BYTES + B_BYTES + SFA_BYTES + (uint32_t)ti.nb_valid * 2048u;
                     mbar_arrive_expect_tx(full, tx);
-                    tma_load_3d(sA, ti.ta, k0, ti.m0, ti.l, full);
-                    tma_load_3d(sB, ti.tb, k0, ti.n0, ti.l, full);
-                    if (DUAL) tma_load_3d(sB + BN * 128, ti.tb2, k0, ti.n0, ti.l, full);
+                    tma_load_3d(sA, ti.ta, kx, ti.m0, ti.l, full);
+                    tma_load_3d(sB, ti.tb, kx, ti.n0, ti.l, full);
+                    if (DUAL) tma_load_3d(sB + BN * 128, ti.tb2, kx, ti.n0, ti.l, full);
                     const size_t koff = (size_t)(k0 / 64) * 512;
                     bulk_g2s(sSFA, ti.sfa_t + koff, 2048u, full);
                     if (DUAL) {
@@ -137,6 +153,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     }
                 }
             }
+#ifdef NVFP4_PROFILE
+            if (p.prof) p.prof[8 * blockIdx.x + 4] = prof_empty;
+#endif
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer (one lane)
@@ -145,7 +164,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             uint32_t it = 0, tile_it = 0;
             bool alive = true;
 #ifdef NVFP4_PROFILE
-            long long prof_acc = 0, prof_full = 0;
+            long long prof_acc = 0, prof_full = 0, prof_lat = 0, prof_late = 0;
             const long long prof_begin = clock64();
 #endif
             for (int t = blockIdx.x; alive && t < total_tiles; t += gridDim.x, tile_it++) {
@@ -171,6 +190,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     bool got;
                     {
                         PROF_T0();
+#ifdef NVFP4_PROFILE
+                        if (!mbar_try_wait(full0 + 8 * slot, (it / STAGES) & 1)) prof_late++;
+#endif
                         got = mbar_wait(full0 + 8 * slot, (it / STAGES) & 1, p.budget_ns);
                         PROF_ADD(prof_full);
                     }
@@ -179,6 +201,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                         alive = false;
                         break;
                     }
+#ifdef NVFP4_PROFILE
+                    prof_lat += clock64() - prof_issue[slot];   // upper bound of the load latency when the stage was waited for
+#endif
                     tc_fence_after_sync();
                     const uint32_t sA = smem0 + slot * STAGE_BYTES;
                     const uint32_t sB = sA + A_BYTES;
@@ -205,9 +230,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             }
 #ifdef NVFP4_PROFILE
             if (p.prof) {
-                p.prof[3 * blockIdx.x + 0] = prof_acc;
-                p.prof[3 * blockIdx.x + 1] = prof_full;
-                p.prof[3 * blockIdx.x + 2] = clock64() - prof_begin;
+                p.prof[8 * blockIdx.x + 0] = prof_acc;
+                p.prof[8 * blockIdx.x + 1] = prof_full;
+                p.prof[8 * blockIdx.x + 2] = clock64() - prof_begin;
+                p.prof[8 * blockIdx.x + 3] = prof_lat;
+                p.prof[8 * blockIdx.x + 5] = prof_late;
+                p.prof[8 * blockIdx.x + 6] = it;
             }
 #endif
         }
@@ -269,6 +297,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // (256 elements = 128 bytes, box_rows, 1), 128-byte swizzle, out-of-range rows read as zero.
 // Encoding costs about a microsecond of host time, which matters for calls whose kernel runs for ten:
 // the last few maps are kept per thread, keyed by everything that goes into them.
+int operand_kshift() {
+    static const int v = [] { const char* e_ = getenv("NVFP4_TMAP_U8"); return (e_ && atoi(e_) != 0) ? 1 : 0; }();
+    return v;
+}
+
 int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L, int box_rows) {
     struct Key { const void* base; int rows, K, L, box; };
     struct Entry { Key k; CUtensorMap m; bool valid; };
@@ -282,17 +315,39 @@ int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L
             return NVFP4_OK;
         }
     }
-    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)rows, (uint64_t)L};
+    // the packed nibbles travel unchanged either way: as 256 four-bit elements or as 128 bytes per row of the box
+    const int ks = operand_kshift();
+    const uint64_t dims[3] = {(uint64_t)(K >> ks), (uint64_t)rows, (uint64_t)L};
     const uint64_t strides[2] = {(uint64_t)(K / 2), (uint64_t)rows * (uint64_t)(K / 2)};
-    const uint32_t box[3] = {256u, (uint32_t)box_rows, 1u};
-    int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims, strides, box,
-                          CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint32_t box[3] = {256u >> ks, (uint32_t)box_rows, 1u};
+    int rc = encode_tiled(map, ks ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims,
+                          strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     Entry& v = cache[victim];
     victim = (victim + 1) % WAYS;
     v.k = Key{base, rows, K, L, box_rows};
     v.m = *map;
     v.valid = true;
+    return NVFP4_OK;
+}
+
+int make_scale_tmap(CUtensorMap* map, const void* base, long atoms) {
+    struct Entry { const void* base; long atoms; CUtensorMap m; bool valid; };
+    constexpr int WAYS = 8;
+    thread_local Entry cache[WAYS] = {};
+    thread_local int victim = 0;
+    for (int i = 0; i < WAYS; i++)
+        if (cache[i].valid && cache[i].base == base && cache[i].atoms == atoms) {
+            *map = cache[i].m;
+            return NVFP4_OK;
+        }
+    const uint64_t dims[2] = {64u, (uint64_t)atoms};
+    const uint64_t strides[1] = {512u};
+    const uint32_t box[2] = {64u, 4u};
+    int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_UINT64, 2, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    cache[victim] = Entry{base, atoms, *map, true};
+    victim = (victim + 1) % WAYS;
     return NVFP4_OK;
 }
 
@@ -317,7 +372,9 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     }
     if (p.total_tiles <= 0) return NVFP4_OK;
     const int grid = p.total_tiles < sm_count(dev) ? p.total_tiles : sm_count(dev);
-    kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, p);
+    GemmParams q = p;
+    q.kshift = operand_kshift();
+    kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, q);
     e = cudaGetLastError();
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
@@ -518,14 +575,21 @@ namespace nvfp4 {
 namespace {
 
 // The problem table of a launch lives in device memory that the library owns: per device a small ring of
-// (pinned host staging buffer, device buffer, event) slots.  A slot is reused only after the launch that read it
-// has finished (its event), so concurrent streams and back-to-back calls never share a table.
+// (pinned host staging buffer, device buffer, events) slots.  A slot is rewritten only after every launch that
+// read it has finished (`done`), so concurrent streams and back-to-back calls never share a table that is being
+// changed.  When the ring wraps onto a slot whose last launch is still running, the host waits for it
+// (cudaEventSynchronize): eight different descriptor arrays may be in flight per device before a call blocks.
+// A repeated call reuses its slot's table; if it comes on another stream than the one that uploaded the table,
+// its launch is ordered after the upload (`uploaded`), and `done` is re-recorded so that it still covers the
+// launches of the earlier streams.
 constexpr int TABLE_SLOTS = 8;
 struct TableSlot {
     GroupEntry* host = nullptr;
     GroupEntry* dev = nullptr;
     int capacity = 0;
-    cudaEvent_t done = nullptr;
+    cudaEvent_t done = nullptr;      // after the latest launch that reads this table (and, transitively, all earlier ones)
+    cudaEvent_t uploaded = nullptr;  // after the host-to-device copy of the table
+    cudaStream_t last_stream = nullptr;  // stream of the latest upload or launch
     bool used = false;
     // the call this slot's device table was built for: an identical call (same pointers and sizes, the usual
     // case when a layer runs again) reuses the table without re-encoding or uploading anything
@@ -553,6 +617,11 @@ int acquire_slot(int dev, int G, TableSlot** out) {
         e = cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming);
         if (e != cudaSuccess) return (int)e;
     }
+    if (!s.uploaded) {
+        e = cudaEventCreateWithFlags(&s.uploaded, cudaEventDisableTiming);
+        if (e != cudaSuccess) return (int)e;
+    }
+    s.used = false;
     if (s.capacity < G) {
         int cap = 64;
         while (cap < G) cap *= 2;
@@ -616,10 +685,23 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
         }
     }
     if (slot) {
+        const bool other_stream = st != slot->last_stream;
+        if (other_stream) {
+            // the table may still be on its way to the device on the stream that built it
+            e = cudaStreamWaitEvent(st, slot->uploaded, 0);
+            if (e != cudaSuccess) return (int)e;
+        }
         p.table = slot->dev; p.G = slot->live; p.total_tiles = slot->tiles;
         const CUtensorMap& dm = slot->host[0].ta;
         int rc2 = slot->bn == 256 ? launch_gemm<256, false, true, 4>(dm, dm, dm, p, st)
                                   : launch_gemm<128, false, true, 6>(dm, dm, dm, p, st);
+        if (other_stream) {
+            // `done` is about to move to this stream: first make this stream's record wait for the launches the
+            // old record stood for, so that the slot is not rewritten while any of them still reads the table
+            e = cudaStreamWaitEvent(st, slot->done, 0);
+            if (e != cudaSuccess) return (int)e;
+            slot->last_stream = st;
+        }
         e = cudaEventRecord(slot->done, st);
         if (rc2) return rc2;
         return e == cudaSuccess ? NVFP4_OK : (int)e;
@@ -643,6 +725,9 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     }
     e = cudaMemcpyAsync(slot->dev, slot->host, sizeof(GroupEntry) * live, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return (int)e;
+    e = cudaEventRecord(slot->uploaded, st);
+    if (e != cudaSuccess) return (int)e;
+    slot->last_stream = st;
     p.table = slot->dev; p.G = live; p.total_tiles = tiles;
     slot->key.assign(groups, groups + G);
     slot->live = live; slot->tiles = tiles; slot->bn = bn;
@@ -666,13 +751,14 @@ extern "C" int nvfp4_shutdown(void) {
     if (cudaGetDevice(&cur) != cudaSuccess) return NVFP4_ERR_INTERNAL;
     for (int dev = 0; dev < 64; dev++) {
         bool any = false;
-        for (const TableSlot& sl : g_rings[dev].slots) any = any || sl.host || sl.dev || sl.done;
+        for (const TableSlot& sl : g_rings[dev].slots) any = any || sl.host || sl.dev || sl.done || sl.uploaded;
         if (!any) continue;
         cudaSetDevice(dev);
         for (TableSlot& sl : g_rings[dev].slots) {
             if (sl.host) cudaFreeHost(sl.host);
             if (sl.dev) cudaFree(sl.dev);
             if (sl.done) cudaEventDestroy(sl.done);
+            if (sl.uploaded) cudaEventDestroy(sl.uploaded);
             sl = TableSlot();
         }
         g_rings[dev].next = 0;
@@ -735,6 +821,13 @@ extern "C" int nvfp4_grouped_gemm_noalloc(const nvfp4_group_t* groups, int G, fl
     if (e != cudaSuccess) return (int)e;
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
     const int bn = wide ? 256 : 128;
+
+    // Under stream capture the copy below would become a graph node that re-reads the shared host image at every
+    // replay, whatever a later call has left there: refuse instead of recording a graph that cannot be trusted.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing((cudaStream_t)stream, &cap);
+    if (e != cudaSuccess) return (int)e;
+    if (cap != cudaStreamCaptureStatusNone) return NVFP4_ERR_UNSUPPORTED;
 
     std::lock_guard<std::mutex> lk(g_static_mu);
     if (!g_static_table_addr[dev]) {

@@ -280,6 +280,24 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
         }
     }
 }
+// Tiled TMA loads issued by a CTA of a pair into its OWN shared memory whose completion bytes are counted on an
+// mbarrier of either CTA of the pair (`bar` is a shared::cluster address from mapa_shared()): this is how the second
+// CTA of a pair tells the leader that its half of a stage has landed, without a thread in between.  Not a
+// multicast: the data goes to the issuing CTA only.
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const void* tmap, int x, int y, int z, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3, "
+        "%4}], [%5];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const void* tmap, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.cta_group::2 [%0], [%1, {%2, %3}], "
+        "[%4];" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
 // Store one word into the shared memory of a CTA of the cluster (address from mapa_shared()).
 __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");

@@ -134,13 +134,24 @@ class GatheredOutput:
         """The local copy as ``[M, N, L]`` (the layout of the reference's ``c``)."""
         return F.batch_last(self.buf)
 
-    def wait_all(self):
-        """Stream-ordered: what follows on the current stream runs after every rank's kernel has finished, so every
-        copy is complete.  (A one-element all-reduce: unlike ``dist.barrier`` it does not block the host.)"""
+    def _stream_barrier(self):
         if self.group is not None and self.world > 1:
             if getattr(self, "_flag", None) is None:
                 self._flag = torch.zeros(1, dtype=torch.float32, device=self.buf.device)
             dist.all_reduce(self._flag, group=self.group)
+
+    def wait_all(self):
+        """Stream-ordered: what follows on the current stream runs after every rank's kernel has finished, so every
+        copy is complete.  (A one-element all-reduce: unlike ``dist.barrier`` it does not block the host.)"""
+        self._stream_barrier()
+
+    def release(self):
+        """Stream-ordered, the other half of the protocol: call it after the consumers of this rank's copy have
+        been enqueued and before the next ``gemm_allgather`` into the same buffer.  What follows on the current
+        stream runs only after every rank has got that far, so no rank's next launch overwrites a copy that a peer
+        is still reading.  ``wait_all`` alone only protects against reading too early.  (Alternating between two
+        ``GatheredOutput`` buffers does the same job without the second barrier.)"""
+        self._stream_barrier()
 
 
 def _ptr_array(ptrs):
@@ -150,7 +161,8 @@ def _ptr_array(ptrs):
 
 def gemm_allgather(shard, out: GatheredOutput, rank: int, alpha: float = 1.0):
     """``shard``: this rank's tuple from ``shard_gemm`` (its ``c`` is not used).  Writes the rank's columns into every
-    rank's copy of ``out``; call ``out.wait_all()`` before reading."""
+    rank's copy of ``out``; call ``out.wait_all()`` before reading, and ``out.release()`` after the readers and before
+    the next launch into the same ``out``."""
     from . import _args, _lib
     a, b, _, _, sfa_p, sfb_p, _ = shard
     m, k2, l = a.shape

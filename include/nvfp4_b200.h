@@ -46,7 +46,8 @@ enum {
  * Replaces custom_kernel of eval/nvfp4_gemv/submission.py:28-54 (tuple of
  * eval/nvfp4_gemv/reference.py:31-49): x is the reference's `b` operand, [L][x_rows][K/2] with the
  * vector in row 0 (x_rows = 128 there), sfx_sw its swizzled scales; c is [L][M].
- * K % 64 == 0, K <= 65536; a, x, scales 16-byte aligned. */
+ * K % 64 == 0 (any K: few 128-row tiles with K <= 65536 take the decode kernel, everything else the tensor-core
+ * streaming kernel, which has no K limit); a, x, scales 16-byte aligned. */
 int nvfp4_gemv(const void* a, const void* x, const void* sfa_sw, const void* sfx_sw, void* c,
                int M, int K, int L, int x_rows, float alpha, void* stream);
 
@@ -77,7 +78,10 @@ int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const v
  * columns [rank*N_local, (rank+1)*N_local) of C and stores every piece of them into the full C buffer
  * [L][M][N_local*world] of EVERY rank: c_all[r] is rank r's buffer as mapped into this process (peer memory:
  * symmetric memory or an IPC mapping; c_all[rank] is the local one), 32-byte aligned; world <= 8.  Plain stores over
- * NVLink, no collective call; the caller orders "all ranks have finished" (a barrier on the stream) before C is read.
+ * NVLink, no collective call.  The caller provides two orderings across ranks: "all ranks have finished" (a
+ * barrier on the stream) before C is read, and "all ranks' readers have finished" (a second barrier, or a second
+ * buffer used in alternation) before the next call into the same buffers - a rank that has passed the first
+ * barrier would otherwise overwrite a copy that a peer is still reading.
  * No counterpart in the reference (a single-GPU harness); replaces gemm + ncclAllGather of the column shards. */
 int nvfp4_gemm_allgather(const void* a, const void* b, const void* sfa_sw, const void* sfb_sw,
                          void* const* c_all, int world, int rank, int M, int N_local, int K, int L,
@@ -110,7 +114,9 @@ int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alpha, void* st
  *    loads the library until the process exits): at most 256 non-empty groups per call, more are refused with
  *    NVFP4_ERR_TOO_MANY_GROUPS.
  *  - It calls no cudaMalloc / cudaFree / cudaHostAlloc and creates no events.  The first call on a device
- *    resolves the array's device address; make that call before any stream capture.
+ *    resolves the array's device address; make that call before any stream capture.  A call on a stream that is
+ *    being captured is refused with NVFP4_ERR_UNSUPPORTED (the table upload reads a host image that later calls
+ *    rewrite, so a recorded copy of it could not be replayed faithfully).
  *  - Every call rewrites the same array (the previous call's entries stay behind, only the first `live`
  *    entries are read): calls that overlap on the GPU - different streams - race; keep them on one stream or
  *    order them yourself.

@@ -233,3 +233,29 @@ int oracle_gemv(const uint8_t *a, const uint8_t *x, const uint8_t *sfa_sw, const
     free(X); free(SX);
     return 0;
 }
+
+/* Dequantise one operand: p:[L][rows][K/2] packed e2m1, sf_sw swizzled e4m3 scales -> out:[L][rows][K] fp32
+ * (value * scale of its 16-element block).  First half of the "dequantise, then fp32 matmul" route, the shape of
+ * computation the reference's oracle has on the GPU (eval/nvfp4_gemm/reference.py:16-27); the matmul half is a
+ * library fp32 GEMM called from nvfp4_oracle.py. */
+int oracle_dequant(const uint8_t *p, const uint8_t *sf_sw, float *out, int rows, int K, int L) {
+    if (rows <= 0 || K <= 0 || K % SF_VEC || L <= 0) return -1;
+    static const float LUT[16] = {0.f, .5f, 1.f, 1.5f, 2.f, 3.f, 4.f, 6.f, -0.f, -.5f, -1.f, -1.5f, -2.f, -3.f, -4.f, -6.f};
+    int kbs = K / SF_VEC;
+    for (int l = 0; l < L; l++) {
+#pragma omp parallel for schedule(static)
+        for (int r = 0; r < rows; r++) {
+            const uint8_t *src = p + ((size_t)l * rows + r) * (K / 2);
+            float *dst = out + ((size_t)l * rows + r) * K;
+            for (int kb = 0; kb < kbs; kb++) {
+                float s = oracle_e4m3_decode(sf_sw[oracle_sf_offset(r, kb, l, rows, K)]);
+                for (int j = 0; j < SF_VEC / 2; j++) {
+                    unsigned b = src[kb * 8 + j];
+                    dst[kb * 16 + 2 * j] = LUT[b & 15] * s;
+                    dst[kb * 16 + 2 * j + 1] = LUT[b >> 4] * s;
+                }
+            }
+        }
+    }
+    return 0;
+}

@@ -87,6 +87,7 @@ def _load():
         lib.oracle_e4m3_decode.restype = f
         lib.oracle_e2m1_decode.argtypes = [ctypes.c_uint]
         lib.oracle_e2m1_decode.restype = f
+        lib.oracle_dequant.argtypes = [u8p, u8p, ctypes.c_void_p, i, i, i]
         lib.oracle_num_threads.restype = i
         lib.oracle_set_num_threads.argtypes = [i]
         _lib = lib
@@ -237,3 +238,68 @@ def np_gemv(a, x, sfa_sw, sfx_sw, alpha: float = 1.0) -> np.ndarray:
     A = np_dequant(a, sfa_sw, M, K, L)
     X = np_dequant(x, sfx_sw, x_rows, K, L)[:, :1]
     return (np.float32(alpha) * _mm(A, X))[:, :, 0].astype(np.float16)
+
+
+# --------------------------------------------------------------------------- dequantise (C, OpenMP) + library fp32 matmul
+# The fastest CPU form of the reference's "dequantise, then matmul" computation: the C dequantiser on all cores, then
+# torch.matmul in fp32.  Every function returns (result, seconds dequantising, seconds in the matmul and epilogue), so
+# the CPU baseline of the bench can list the two phases apart.
+
+def c_dequant(p, sf_sw, rows: int, K: int, L: int) -> np.ndarray:
+    """Packed operand + swizzled scales -> [L, rows, K] float32 (oracle_dequant in nvfp4_oracle.c)."""
+    p, sf_sw = _u8(p), _u8(sf_sw)
+    assert p.size == L * rows * (K // 2) and sf_sw.size >= sf_bytes(rows, K, L)
+    out = np.empty((L, rows, K), dtype=np.float32)
+    rc = _load().oracle_dequant(_ptr(p), _ptr(sf_sw), _ptr(out), rows, K, L)
+    assert rc == 0, rc
+    return out
+
+
+def dq_gemm(a, b, sfa_sw, sfb_sw, alpha: float = 1.0):
+    import time
+    L, M, K2 = a.shape
+    N, K = b.shape[1], 2 * K2
+    t0 = time.perf_counter()
+    A, B = c_dequant(a, sfa_sw, M, K, L), c_dequant(b, sfb_sw, N, K, L)
+    t1 = time.perf_counter()
+    c = (np.float32(alpha) * _mm(A, B)).astype(np.float16)
+    return c, t1 - t0, time.perf_counter() - t1
+
+
+def dq_dual_gemm(a, b1, b2, sfa_sw, sfb1_sw, sfb2_sw, alpha: float = 1.0):
+    import time
+    import torch
+    L, M, K2 = a.shape
+    N, K = b1.shape[1], 2 * K2
+    t0 = time.perf_counter()
+    A, B1, B2 = c_dequant(a, sfa_sw, M, K, L), c_dequant(b1, sfb1_sw, N, K, L), c_dequant(b2, sfb2_sw, N, K, L)
+    t1 = time.perf_counter()
+    r1 = torch.from_numpy(_mm(A, B1)).mul_(float(alpha))
+    r2 = torch.from_numpy(_mm(A, B2)).mul_(float(alpha))
+    c = torch.nn.functional.silu(r1).mul_(r2).to(torch.float16).numpy()
+    return c, t1 - t0, time.perf_counter() - t1
+
+
+def dq_gemv(a, x, sfa_sw, sfx_sw, alpha: float = 1.0):
+    import time
+    L, M, K2 = a.shape
+    K, x_rows = 2 * K2, x.shape[1]
+    t0 = time.perf_counter()
+    A, X = c_dequant(a, sfa_sw, M, K, L), c_dequant(x, sfx_sw, x_rows, K, L)[:, :1]
+    t1 = time.perf_counter()
+    c = (np.float32(alpha) * _mm(A, X))[:, :, 0].astype(np.float16)
+    return c, t1 - t0, time.perf_counter() - t1
+
+
+def dq_grouped_gemm(groups, alpha: float = 1.0):
+    out, td, tm = [], 0.0, 0.0
+    for a, b, sfa_sw, sfb_sw in groups:
+        a, b = _u8(a), _u8(b)
+        if a.shape[0] == 0:
+            out.append(np.empty((0, b.shape[0]), dtype=np.float16))
+            continue
+        c, d, m = dq_gemm(a[None], b[None], sfa_sw, sfb_sw, alpha)
+        out.append(c[0])
+        td += d
+        tm += m
+    return out, td, tm

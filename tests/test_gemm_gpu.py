@@ -7,12 +7,14 @@ from _util import dual_oracle_args, gemm_oracle_args, out_np, to_device
 
 pytestmark = pytest.mark.gpu
 
-# the harness's GEMM correctness list (m, n, k, l); the largest one is left to test_large_* below
+# the harness's correctness lists (m, n, k, l): every line of eval/nvfp4_gemm/tests.txt and every distinct line of
+# eval/nvfp4_dual_gemm/tests.txt
 GEMM_TESTS = [(128, 256, 256, 1), (128, 1536, 7168, 1), (128, 3072, 1536, 1), (256, 7168, 256, 1),
-              (256, 7168, 2048, 1), (384, 7168, 2304, 1), (512, 512, 7168, 1), (512, 4096, 512, 1),
-              (512, 1536, 7168, 1)]
-DUAL_TESTS = [(256, 512, 256, 1), (1536, 512, 7168, 1), (3072, 1024, 1536, 1), (7168, 1024, 256, 1),
-              (512, 768, 7168, 1), (4096, 768, 512, 1), (7168, 384, 2304, 1)]
+              (256, 7168, 2048, 1), (2304, 4608, 7168, 1), (384, 7168, 2304, 1), (512, 512, 7168, 1),
+              (512, 4096, 512, 1), (512, 1536, 7168, 1)]
+DUAL_TESTS = [(1536, 512, 7168, 1), (256, 512, 256, 1), (3072, 1024, 1536, 1), (7168, 1024, 256, 1),
+              (7168, 2304, 2048, 1), (4608, 384, 7168, 1), (7168, 384, 2304, 1), (512, 768, 7168, 1),
+              (4096, 768, 512, 1)]
 
 
 def _status_ok():
@@ -105,6 +107,43 @@ def test_large_gemm_rows_against_oracle(oracle):
     got = torch.from_numpy(out_np(c_half)[:, band])
     assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
     assert check.max_delta_ok(got, want)[0]
+
+
+def test_large_gemm_whole_output_against_scaled_mm():
+    """8192^3, N(0,1)-quantised operands: every element against the reference's arithmetic
+    (torch._scaled_mm, eval/nvfp4_gemm/reference.py:16-27) under the harness's rtol = atol = 1e-3."""
+    from eval_test_b200 import check, inputs, nvfp4_gemm, reference_check
+    data = inputs.gemm_quantized(8192, 8192, 8192, 1, seed=0, device="cuda")
+    got = nvfp4_gemm.custom_kernel(data).clone()
+    _status_ok()
+    want = reference_check.ref_gemm(data)
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
+def test_large_dual_gemm_rows_against_oracle_and_whole_output_against_scaled_mm(oracle):
+    """The SwiGLU up-projection configuration, M = 4096, N = 14336, K = 4096, N(0,1)-quantised operands: two
+    128-row bands of the output against the CPU oracle, every element against the reference's arithmetic (two fp32
+    torch._scaled_mm products, silu(r1) * r2 in fp32, one rounding: eval/nvfp4_dual_gemm/reference.py:24-44), both
+    under the harness's rtol = atol = 1e-3 and under max|d| <= 1e-2 max|ref|."""
+    from _util import operand_np, scales_np
+    from eval_test_b200 import check, inputs, nvfp4_dual_gemm, reference_check
+    m, n, k = 4096, 14336, 4096
+    data = inputs.dual_gemm_quantized(m, n, k, 1, seed=0, device="cuda")
+    a, b1, b2, _, _, _, sfa_p, sfb1_p, sfb2_p, c = data
+    got = nvfp4_dual_gemm.custom_kernel(data).clone()
+    _status_ok()
+    want = reference_check.ref_dual_gemm(data)
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+    sfa_blocks = scales_np(sfa_p).reshape(m // 128, -1)
+    for blk in (0, 23):
+        band = slice(128 * blk, 128 * (blk + 1))
+        ref = torch.from_numpy(oracle.c_dual_gemm(operand_np(a)[:, band], operand_np(b1), operand_np(b2),
+                                                  sfa_blocks[blk].reshape(-1), scales_np(sfb1_p), scales_np(sfb2_p)))
+        mine = torch.from_numpy(out_np(got)[:, band])
+        assert check.verbose_allclose(mine, ref, rtol=1e-3, atol=1e-3) == []
+        assert check.max_delta_ok(mine, ref)[0]
 
 
 def test_gemm_bad_arguments():

@@ -75,6 +75,73 @@ def test_grouped_poisson_sizes_wide_tiles(oracle):
             assert check.verbose_allclose(torch.from_numpy(gg), torch.from_numpy(w), rtol=1e-3, atol=1e-3) == []
 
 
+@pytest.mark.parametrize("forced_empty", [(), (3, 17, 18, 40, 63)])
+def test_grouped_moe_configuration_full_size(oracle, forced_empty):
+    """The MoE expert-layer configuration at full size: 64 groups, N = 4096, K = 7168, M_g ~ Poisson(128) clipped
+    to [0, 1024] from numpy's default_rng(0); the second variant forces five groups to M = 0 (a seeded draw never
+    gives an empty group).  Every group against the reference's arithmetic (torch._scaled_mm per group,
+    eval/nvfp4_grouped_gemm/reference.py:48-74), sampled groups against the CPU oracle, under rtol = atol = 1e-3 and
+    max|d| <= 1e-2 max|ref|; outputs of empty groups stay empty and nothing else is touched."""
+    from _util import operand_np, scales_np
+    from eval_test_b200 import check, inputs, reference_check
+    g = 64
+    m = inputs.poisson_group_sizes(g, 128.0, 0, 1024, seed=0)
+    for i in forced_empty:
+        m[i] = 0
+    data = inputs.grouped_gemm_quantized(m, [4096] * g, [7168] * g, g, seed=0, device="cuda")
+    got = _run(data)
+    want = reference_check.ref_grouped_gemm(data)
+    abc, _, sfs_p, _ = data
+    for i, (mine, ref) in enumerate(zip(got, want)):
+        assert mine.shape == (m[i], 4096)
+        if m[i]:
+            mine_t, ref_t = torch.from_numpy(mine), ref[:, :, 0].cpu()
+            assert check.verbose_allclose(mine_t, ref_t, rtol=1e-3, atol=1e-3) == [], i
+            assert check.max_delta_ok(mine_t, ref_t)[0], i
+    for i in (0, 19, 41, 62):
+        (a, b, _), (sa, sb) = abc[i], sfs_p[i]
+        ref = oracle.c_gemm(operand_np(a), operand_np(b), scales_np(sa), scales_np(sb))[0]
+        assert check.verbose_allclose(torch.from_numpy(got[i]), torch.from_numpy(ref), rtol=1e-3, atol=1e-3) == [], i
+
+
+def test_grouped_same_call_again_and_from_a_second_stream(oracle):
+    """The library reuses a problem table when a call repeats an earlier one (same pointers and sizes).  The
+    repeat may come on another stream while the first call's table upload is still queued, so the reuse must be
+    ordered after the upload; outputs are poisoned between the calls and compared with the oracle bit for bit."""
+    from eval_test_b200 import inputs, nvfp4_grouped_gemm
+    data = to_device(inputs.grouped_gemm_reference_style([200, 96, 0, 384], [256, 512, 256, 256], [512, 256, 256, 768],
+                                                         4, seed=31, device="cpu"))
+    want = oracle.c_grouped_gemm(grouped_oracle_args(data))
+    side = torch.cuda.Stream()
+
+    def poison():
+        for (_, _, c) in data[0]:
+            c.fill_(float("nan"))
+
+    def verify():
+        torch.cuda.synchronize()
+        for (_, _, c), w in zip(data[0], want):
+            assert np.array_equal(out_np(c)[0].view(np.uint16), w.view(np.uint16))
+
+    poison()
+    torch.cuda.synchronize()
+    # a long copy keeps the first stream busy, so its table upload and launch are still queued when the
+    # second stream asks for the same table
+    busy = torch.empty(1 << 28, dtype=torch.uint8, device="cuda")
+    for _ in range(8):
+        busy.fill_(1)
+    nvfp4_grouped_gemm.custom_kernel(data)
+    with torch.cuda.stream(side):
+        nvfp4_grouped_gemm.custom_kernel(data)
+    verify()
+    for stream in (torch.cuda.current_stream(), side, torch.cuda.current_stream()):
+        poison()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(stream):
+            nvfp4_grouped_gemm.custom_kernel(data)
+        verify()
+
+
 def test_grouped_repeated_calls_and_streams(oracle):
     """More back-to-back calls than the library has problem-table slots, on two streams: every call's table
     must stay intact until its launch has read it."""

@@ -21,6 +21,48 @@ def test_usage_and_bad_spec_exit_codes(tmp_path, capsys):
     capsys.readouterr()
 
 
+def test_sampling_modes_follow_the_reference_runners():
+    """GEMM one call per sample; GEMV and dual GEMM batches of 50; grouped GEMM batches of 15
+    (eval/nvfp4_gemm/eval.py:13, eval/nvfp4_gemv/eval.py:11-12, eval/nvfp4_dual_gemm/eval.py:11-12,
+    eval/common/eval_base.py:141-142)."""
+    from eval_test_b200 import runner
+    assert runner.SAMPLING == {"nvfp4_gemm": (False, 1), "nvfp4_gemv": (True, 50), "nvfp4_dual_gemm": (True, 50),
+                               "nvfp4_grouped_gemm": (True, 15)}
+
+
+def test_report_parses_a_log_and_renders_floors():
+    from eval_test_b200 import report
+    log = "\n".join([
+        "benchmark-count: 1", "benchmark.0.spec: m: 128; n: 7168; k: 16384; l: 1; seed: 1111", "benchmark.0.runs: 5",
+        "benchmark.0.mean: 29000.0", "benchmark.0.std: 100.0", "benchmark.0.err: 44.7", "benchmark.0.best: 28000.0",
+        "benchmark.0.worst: 30000.0", "check: pass"])
+    data = report.parse_log(log)
+    assert data["check"] == "pass" and data["benchmark_count"] == 1 and data["benchmarks"][0]["runs"] == "5"
+    by, fl = report.work_of("nvfp4_gemm", {"m": 128, "n": 7168, "k": 16384, "l": 1})
+    assert fl == 2 * 128 * 7168 * 16384
+    assert by == (128 + 7168) * (16384 // 2 + 16384 // 16) + 2 * 128 * 7168
+    text = report.format_report(data, "benchmark", "nvfp4_gemm")
+    assert "success" in text and "29.0" in text and "28.0" in text
+    tests = report.parse_log("test-count: 2\ntest.0.spec: m: 1\ntest.0.status: pass\ntest.1.spec: m: 2\n"
+                             "test.1.status: fail\ntest.1.error: mismatch\ncheck: fail")
+    text = report.format_report(tests, "test", "nvfp4_gemm")
+    assert "failure" in text and "fail: mismatch" in text
+    by_g, fl_g = report.work_of("nvfp4_grouped_gemm", {"m": [0, 100], "n": [256, 256], "k": [512, 512]})
+    assert fl_g == 2 * 100 * 256 * 512
+
+
+def test_stop_rule_needs_three_samples_and_100_ms():
+    import time
+    from eval_test_b200 import runner
+    start = time.perf_counter_ns()
+    assert not runner._enough([1.0, 1.0, 1.0], 2, start, 1e9)            # wall time below 100 ms
+    long_ago = start - int(2e8)
+    assert not runner._enough([1.0, 1.0], 1, long_ago, 1e9)             # fewer than three samples
+    assert runner._enough([100.0, 100.0, 100.0], 2, long_ago, 1e9)      # error of the mean below 0.1 %
+    assert not runner._enough([100.0, 150.0, 50.0], 2, long_ago, 1e9)   # noisy, budget left
+    assert runner._enough([100.0, 150.0, 50.0], 2, long_ago, 200.0)     # budget used up
+
+
 def _run(mode, task, text, tmp_path, monkeypatch):
     from eval_test_b200 import runner
     specfile = tmp_path / "cases.txt"
@@ -53,7 +95,23 @@ def test_test_mode_passes_against_scaled_mm(task, text, tmp_path, monkeypatch):
 
 
 @pytest.mark.gpu
-def test_benchmark_mode_reports_stats(tmp_path, monkeypatch):
-    code, lines = _run("benchmark", "nvfp4_gemv", "m: 7168; k: 2048; l: 4; seed: 1111", tmp_path, monkeypatch)
+@pytest.mark.parametrize("mode,task,text", [
+    ("benchmark", "nvfp4_gemv", "m: 7168; k: 2048; l: 4; seed: 1111"),          # batches of 50
+    ("benchmark", "nvfp4_gemm", "m: 128; n: 4096; k: 7168; l: 1; seed: 1111"),   # one call per sample
+    ("leaderboard", "nvfp4_gemm", "m: 128; n: 7168; k: 2048; l: 1; seed: 1111"), # fresh inputs and a re-check per repeat
+    ("leaderboard", "nvfp4_grouped_gemm", "m: [128, 384]; n: [4096, 4096]; k: [1536, 1536]; g: 2; seed: 1111"),
+])
+def test_benchmark_modes_report_stats(mode, task, text, tmp_path, monkeypatch):
+    code, lines = _run(mode, task, text, tmp_path, monkeypatch)
     assert code == 0, lines
+    assert lines["check"] == "pass" and "benchmark.0.status" not in lines
     assert int(lines["benchmark.0.runs"]) >= 3 and 1e3 < float(lines["benchmark.0.mean"]) < 1e8
+
+
+@pytest.mark.gpu
+def test_profile_mode_logs_a_table(tmp_path, monkeypatch):
+    import base64
+    code, lines = _run("profile", "nvfp4_gemm", "m: 128; n: 256; k: 256; l: 1; seed: 1111", tmp_path, monkeypatch)
+    assert code == 0, lines
+    table = base64.b64decode(lines["benchmark.0.report"], b"+*").decode()
+    assert "gemm" in table

@@ -11,7 +11,7 @@ import numpy as np
 import pytest
 import torch
 
-from _util import to_device
+from _util import grouped_oracle_args, out_np, to_device
 
 pytestmark = pytest.mark.gpu
 
@@ -56,6 +56,25 @@ def test_noalloc_entry_matches_regular_entry_twice():
             assert g.shape == w.shape
             assert not torch.isnan(g).any()
             assert torch.equal(g.view(torch.int16), w.view(torch.int16))
+    assert _lib.device_status(torch.cuda.current_device()) == 0
+
+
+def test_noalloc_entry_wide_tiles_against_the_oracle(oracle):
+    """Every N a multiple of 256, so both entry points take the 256-column tile instantiation; dyadic inputs, so
+    the fixed-table entry point must reproduce the CPU oracle (and the regular entry point) bit for bit; again on
+    two calls in a row, the second with fewer groups."""
+    from eval_test_b200 import _lib, inputs
+    lib = _lib.load()
+    first = to_device(inputs.grouped_gemm_reference_style([200, 0, 96, 384], [256, 512, 768, 256], [512, 256, 256, 768],
+                                                          4, seed=23, device="cpu"))
+    second = to_device(inputs.grouped_gemm_reference_style([130, 64], [512, 256], [256, 1024], 2, seed=24,
+                                                           device="cpu"))
+    for data in (first, second):
+        want = oracle.c_grouped_gemm(grouped_oracle_args(data))
+        for entry in (lib.nvfp4_grouped_gemm_noalloc, lib.nvfp4_grouped_gemm):
+            got = _run(entry, data)
+            for g, w in zip(got, want):
+                assert np.array_equal(out_np(g)[0].view(np.uint16), w.view(np.uint16))
     assert _lib.device_status(torch.cuda.current_device()) == 0
 
 
