@@ -134,7 +134,7 @@ class GemmWorkload:
     metric = "nvfp4_gemm_tflops"
     unit, per = "TFLOPS", 1e12
     dtype = "e2m1 x ue4m3 scales on tcgen05 (kind::mxf4nvf4), fp32 accumulate, fp16 out"
-    bound, kernel, scaling = "tensor", "gemm_kernel", "strong"
+    bound, kernel, scaling = "tensor", "gemm_pair_kernel", "strong"
     alpha = 0.5
 
     def __init__(self, m=8192, n=8192, k=8192):
@@ -200,6 +200,7 @@ class GemmGatherWorkload(GemmWorkload):
     an NCCL all-gather of the column shards.  The roofline target is the slower of the rank's flops at the tensor
     peak and the bytes the rank must send at 770 GB/s (measured peer-copy bandwidth per direction)."""
     metric = "nvfp4_gemm_allgather_tflops"
+    kernel = "gemm_kernel"
     nvlink_gbs = 770.0
 
     def __init__(self, fused=True, m=8192, n=8192, k=8192):
@@ -226,10 +227,35 @@ class GemmGatherWorkload(GemmWorkload):
     def run(self, data):
         from eval_test_b200 import nvfp4_gemm, shard
         if self.fused:
+            # wait_all() orders "every rank has written" before the next thing on the stream; nothing reads C between
+            # two steps here, so the second barrier of the protocol (GatheredOutput.release) has no reader to wait for
             shard.gemm_allgather(data, self.out, self.rank, alpha=self.alpha)
             self.out.wait_all()
             return self.out.view()
-        return shard.gather_cols(nvfp4_gemm.custom_kernel(data, alpha=self.alpha), self.world)
+        self.last = shard.gather_cols(nvfp4_gemm.custom_kernel(data, alpha=self.alpha), self.world)
+        return self.last
+
+    def verify(self, data, ctx) -> str:
+        """Every rank rebuilds all ranks' column shards of B from their seeds, computes the unsharded product with the
+        plain kernel and compares its gathered copy of C with it bit for bit; "ok" only if all ranks agree."""
+        import torch
+        from eval_test_b200 import inputs, nvfp4_gemm
+        a, _, sfa, _, sfa_p, _, _ = data
+        dev, n_loc = a.device, self.n // self.world
+        self.run(data)
+        torch.cuda.synchronize()
+        got = (self.out.view() if self.fused else self.last).clone()
+        good = True
+        for r in range(self.world):
+            g = torch.Generator(device=dev).manual_seed(1000 + r)
+            b, sfb, sfb_p = inputs.quantized_operand(1, n_loc, self.k, g, dev)
+            c = torch.empty((1, self.m, n_loc), dtype=torch.float16, device=dev).permute(1, 2, 0)
+            nvfp4_gemm.custom_kernel((a, b, sfa, sfb, sfa_p, sfb_p, c), alpha=self.alpha)
+            good = good and torch.equal(got[:, r * n_loc:(r + 1) * n_loc].view(torch.int16), c.view(torch.int16))
+        flag = torch.tensor([1.0 if good else 0.0], device=dev)
+        if self.world > 1:
+            ctx.dist.all_reduce(flag, op=ctx.dist.ReduceOp.MIN)
+        return "ok" if bool(flag.item() == 1.0) else "MISMATCH"
 
     def io(self, data):
         ins, outs = super().io(data)
@@ -251,7 +277,7 @@ class DualGemmWorkload(GemmWorkload):
     """SwiGLU up-projection: C = silu(A.B1) * (A.B2), A 4096 x 4096, B1 and B2 14336 x 4096."""
     name = "dual_gemm_m4096_n14336_k4096"
     metric = "nvfp4_dual_gemm_tflops"
-    kernel = "gemm_kernel"
+    kernel = "gemm_pair_kernel"
     alpha = 1.0
 
     def __init__(self, m=4096, n=14336, k=4096):
@@ -314,6 +340,7 @@ class DualGemmNvfp4Workload(DualGemmWorkload):
     name = "dual_gemm_nvfp4out_m4096_n14336_k4096"
     metric = "nvfp4_dual_gemm_nvfp4out_tflops"
     dtype = "e2m1 x ue4m3 scales on tcgen05 (kind::mxf4nvf4), fp32 accumulate, fp16 rounding, NVFP4 out"
+    kernel = "gemm_kernel"
 
     def small(self):
         return DualGemmNvfp4Workload(m=2048, n=7168, k=4096)
@@ -570,6 +597,7 @@ def _host_threads() -> int:
 def _time_cpu(fn, budget_s=8.0, max_runs=10):
     """One warm-up run (thread pools, page faults), then up to `max_runs` timed runs within the budget.  Returns the
     per-run seconds and, for routes that report them, the (dequantise, matmul) phase times."""
+    time.sleep(0.3)          # let the worker threads of whatever ran before (another OpenMP runtime's pool) go idle
     t0 = time.perf_counter()
     fn()
     first = time.perf_counter() - t0
@@ -604,8 +632,8 @@ def cpu_baseline(wl, data):
     for route, fn, units, what in wl.cpu_samples(data):
         runs, phases = _time_cpu(fn)
         med = _median(runs)
-        rec = {"value": units / med / wl.per, "seconds": med, "runs": len(runs), "spread": (max(runs) - min(runs)) / med,
-               "sample": what}
+        rec = {"value": units / med / wl.per, "best": units / min(runs) / wl.per, "seconds": med, "runs": len(runs),
+               "spread": (max(runs) - min(runs)) / med, "sample": what}
         if phases:
             rec["dequantise_s"] = _median([p[0] for p in phases])
             rec["matmul_s"] = _median([p[1] for p in phases])
@@ -666,7 +694,8 @@ def run_reference(args, names):
         return
     head = _reference_record(WORKLOADS[names[0]](), args, args.steps, args.warmup)
     if len(names) > 1:
-        head["workloads"] = {n: _reference_record(WORKLOADS[n](), args, max(1, min(args.steps, 5)), 1) for n in names[1:]}
+        head["workloads"] = {n: _reference_record(WORKLOADS[n](), args, max(1, min(args.steps, 5)), 1)
+                             for n in names[1:] if not n.startswith("gemm_gather")}
     print(json.dumps(head), flush=True)
 
 
@@ -764,13 +793,14 @@ def measure(wl, ctx, args, with_cpu=True):
             total_ms = sum(b.elapsed_time(e) for b, e in pairs)
         # ---- untimed continuation of the same launches, so that NVML sees the clock this workload settles at ----
         t0 = time.perf_counter()
-        while time.perf_counter() - t0 < 0.25:
+        while not args.small and time.perf_counter() - t0 < 0.25:
             for _ in range(20):
                 wl.run(data)
             torch.cuda.synchronize()
     kern_ms = total_ms / args.steps
     status = _lib.device_status(ctx.local_rank)
     assert status == 0, f"device status {status}: {_lib.strerror(status)}"
+    check = wl.verify(data, ctx) if hasattr(wl, "verify") else None
 
     # ---- end to end: pinned host inputs -> device, kernel, outputs -> host, every step ----
     def flat(t):
@@ -843,6 +873,8 @@ def measure(wl, ctx, args, with_cpu=True):
                     "steps": e2e_steps},
             "gpu_launches": args.steps, "clocks": clocks.summary(),
         }
+        if check is not None:
+            line["allgather_check"] = check
         if hasattr(wl, "flops"):            # an HBM-bound GEMM: the flop rate beside the byte rate
             line["tflops"] = wl.flops() / (ms_per_step * 1e-3) / 1e12
         if hasattr(wl, "target_us"):   # compute + collective: achieved time against the slower of the two floors
@@ -876,7 +908,8 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--small", action="store_true", help="shrink the workload (profiler captures); not a bench value")
     args = ap.parse_args()
-    names = list(DEFAULT_SET) + (["gemv_rowsplit"] if args.gpus > 1 else []) if args.workload == "all" else [args.workload]
+    multi = ["gemv_rowsplit", "gemm_gather_fused", "gemm_gather_nccl"] if args.gpus > 1 else []
+    names = list(DEFAULT_SET) + multi if args.workload == "all" else [args.workload]
 
     if args.impl == "reference":
         run_reference(args, names)

@@ -62,7 +62,6 @@ struct GemmParams {
     const GroupEntry* table;  // grouped GEMM only: G entries, empty groups left out
     int G;
     int total_tiles;
-    int kshift = 0;           // innermost TMA coordinate = K element index >> kshift (1: operand maps count bytes)
 #ifdef NVFP4_PROFILE
     unsigned long long* prof = nullptr;  // per CTA: cycles the MMA issuer spent waiting for accumulators / for data / in total
 #endif
@@ -265,7 +264,9 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, boo
         tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
-            if (CLUSTER) mbar_arrive_cluster(ovl_free);
+            // "these columns have been read" (tcgen05.wait::ld above): no memory of this thread is published, so the
+            // signal to the other CTA needs no release (which cost about 1 400 cycles per tile in the pair kernel)
+            if (CLUSTER) mbar_arrive_cluster_relaxed(ovl_free);
             else mbar_arrive(ovl_free);
         }
     }
@@ -298,9 +299,7 @@ int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L
 // Tensor map over a swizzled scale buffer seen as rows of one 512-byte atom each: dimensions (64 x 8 bytes, atoms),
 // box (64, 4) = the four atoms of one 256-element K step of one 128-row block, which are consecutive in memory.
 int make_scale_tmap(CUtensorMap* map, const void* base, long atoms);
-// 0 when the operand maps count 4-bit elements, 1 when they count bytes (NVFP4_TMAP_U8=1): what a launcher puts
-// into GemmParams::kshift.
-int operand_kshift();
+
 
 // CTA-pair kernels (gemm_pair_sm100.cu).  pair_tiles_wanted(): true when the shape suits them (M >= 256, enough
 // 256-row tiles to fill the machine).  launch_gemm_pair(): maps with 128-row boxes.

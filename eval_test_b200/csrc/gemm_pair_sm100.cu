@@ -135,22 +135,21 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t sSFA = sB + PAIR_B_BYTES;
                     const uint32_t sSFB = sSFA + PAIR_SFA_BYTES;
                     const int k0 = kit * BK;
-                    const int kx = k0 >> p.kshift;
                     const int ka = k0 / 64;
                     // the leader announces the bytes of BOTH CTAs.  Rows of A beyond M (second CTA of the last row
                     // tile) read as zeros; their scale block does not exist and is not fetched
                     if (rank == 0)
                         mbar_arrive_expect_tx(full0 + 8 * slot, 2u * (PAIR_A_BYTES + PAIR_B_BYTES + PAIR_SFB_BYTES) +
                                                                     PAIR_SFA_BYTES + (peer_rows_exist ? PAIR_SFA_BYTES : 0u));
-                    tma_load_3d_pair(sA, &tmap_a, kx, m0, tc.l, full);
+                    tma_load_3d_pair(sA, &tmap_a, k0, m0, tc.l, full);
                     if (a_rows_exist) tma_load_2d_pair(sSFA, &tmap_sfa, 0, atom_a + ka, full);
                     if (DUAL) {
                         // leader keeps the B1 tile, peer the B2 tile; both need both scale blocks
-                        tma_load_3d_pair(sB, rank == 0 ? &tmap_b : &tmap_b2, kx, n0, tc.l, full);
+                        tma_load_3d_pair(sB, rank == 0 ? &tmap_b : &tmap_b2, k0, n0, tc.l, full);
                         tma_load_2d_pair(sSFB, &tmap_sfb, 0, atom_b + ka, full);
                         tma_load_2d_pair(sSFB + 2048u, &tmap_sfb2, 0, atom_b + ka, full);
                     } else {
-                        tma_load_3d_pair(sB, &tmap_b, kx, n0 + (int)rank * 128, tc.l, full);
+                        tma_load_3d_pair(sB, &tmap_b, k0, n0 + (int)rank * 128, tc.l, full);
                         tma_load_2d_pair(sSFB, &tmap_sfb, 0, atom_b + ka, full);
                         tma_load_2d_pair(sSFB + 2048u, &tmap_sfb, 0, atom_b + atoms_per_block + ka, full);
                     }
@@ -253,7 +252,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 epilogue_tile<BN, DUAL, 0, OV_CHUNKS, true>(t_lane, crow, row < p.M, n0, p.N, p.alpha, l_ovl_free, lane);
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(l_acc_empty0 + 8 * buf);
+            if (lane == 0) mbar_arrive_cluster_relaxed(l_acc_empty0 + 8 * buf);   // accumulator read out (see ovl_free)
         }
     }
 
@@ -270,9 +269,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 namespace {
 
 template <bool DUAL>
+int configure(int dev) {
+    static bool done[64] = {};
+    if (done[dev]) return NVFP4_OK;
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)PAIR_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    done[dev] = true;
+    return NVFP4_OK;
+}
+
+template <bool DUAL>
 int max_pairs(int dev) {
     static int cached[64] = {};
     if (cached[dev]) return cached[dev];
+    // the occupancy query fails for more dynamic shared memory than the kernel has been allowed so far
+    if (configure<DUAL>(dev) != NVFP4_OK) return -1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * sm_count(dev));
     cfg.blockDim = dim3(GEMM_THREADS);
@@ -289,17 +301,6 @@ int max_pairs(int dev) {
     }
     cached[dev] = n > 0 ? n : -1;
     return cached[dev];
-}
-
-template <bool DUAL>
-int configure(int dev) {
-    static bool done[64] = {};
-    if (done[dev]) return NVFP4_OK;
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)PAIR_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    done[dev] = true;
-    return NVFP4_OK;
 }
 
 template <bool DUAL>
@@ -326,8 +327,6 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    GemmParams q = p;
-    q.kshift = operand_kshift();
     const long ka = p.K / 64;
     CUtensorMap tsa, tsb, tsb2;
     rc = make_scale_tmap(&tsa, p.sfa, (long)p.L * ((p.M + 127) / 128) * ka);
@@ -339,7 +338,7 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
         rc = make_scale_tmap(&tsb2, p.sfb2, (long)p.L * (p.N / 128) * ka);
         if (rc) return rc;
     }
-    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<DUAL>, ta, tb, tb2, tsa, tsb, tsb2, q);
+    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<DUAL>, ta, tb, tb2, tsa, tsb, tsb2, p);
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
 

@@ -136,12 +136,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
                     const uint32_t sSFA = sB + B_BYTES;
                     const uint32_t sSFB = sSFA + SFA_BYTES;
                     const int k0 = kit * BK;
-                    const int kx = k0 >> p.kshift;
                     const uint32_t tx = A_BYTES + B_BYTES + SFA_BYTES + (uint32_t)ti.nb_valid * 2048u;
                     mbar_arrive_expect_tx(full, tx);
-                    tma_load_3d(sA, ti.ta, kx, ti.m0, ti.l, full);
-                    tma_load_3d(sB, ti.tb, kx, ti.n0, ti.l, full);
-                    if (DUAL) tma_load_3d(sB + BN * 128, ti.tb2, kx, ti.n0, ti.l, full);
+                    tma_load_3d(sA, ti.ta, k0, ti.m0, ti.l, full);
+                    tma_load_3d(sB, ti.tb, k0, ti.n0, ti.l, full);
+                    if (DUAL) tma_load_3d(sB + BN * 128, ti.tb2, k0, ti.n0, ti.l, full);
                     const size_t koff = (size_t)(k0 / 64) * 512;
                     bulk_g2s(sSFA, ti.sfa_t + koff, 2048u, full);
                     if (DUAL) {
@@ -297,11 +296,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 // (256 elements = 128 bytes, box_rows, 1), 128-byte swizzle, out-of-range rows read as zero.
 // Encoding costs about a microsecond of host time, which matters for calls whose kernel runs for ten:
 // the last few maps are kept per thread, keyed by everything that goes into them.
-int operand_kshift() {
-    static const int v = [] { const char* e_ = getenv("NVFP4_TMAP_U8"); return (e_ && atoi(e_) != 0) ? 1 : 0; }();
-    return v;
-}
-
 int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L, int box_rows) {
     struct Key { const void* base; int rows, K, L, box; };
     struct Entry { Key k; CUtensorMap m; bool valid; };
@@ -315,13 +309,13 @@ int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L
             return NVFP4_OK;
         }
     }
-    // the packed nibbles travel unchanged either way: as 256 four-bit elements or as 128 bytes per row of the box
-    const int ks = operand_kshift();
-    const uint64_t dims[3] = {(uint64_t)(K >> ks), (uint64_t)rows, (uint64_t)L};
+    // (describing the same bytes as a UINT8 tensor with 128-byte rows instead of 256 four-bit elements was measured
+    // at the same speed: the packed nibbles travel unchanged either way)
+    const uint64_t dims[3] = {(uint64_t)K, (uint64_t)rows, (uint64_t)L};
     const uint64_t strides[2] = {(uint64_t)(K / 2), (uint64_t)rows * (uint64_t)(K / 2)};
-    const uint32_t box[3] = {256u >> ks, (uint32_t)box_rows, 1u};
-    int rc = encode_tiled(map, ks ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims,
-                          strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    const uint32_t box[3] = {256u, (uint32_t)box_rows, 1u};
+    int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims, strides, box,
+                          CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     Entry& v = cache[victim];
     victim = (victim + 1) % WAYS;
@@ -372,9 +366,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     }
     if (p.total_tiles <= 0) return NVFP4_OK;
     const int grid = p.total_tiles < sm_count(dev) ? p.total_tiles : sm_count(dev);
-    GemmParams q = p;
-    q.kshift = operand_kshift();
-    kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, q);
+    kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, p);
     e = cudaGetLastError();
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
@@ -406,9 +398,10 @@ extern "C" int nvfp4_gemm(const void* a, const void* b, const void* sfa_sw, cons
     // 256-wide tiles when N allows and they still fill the machine, else 128-wide
     const long tiles256 = (long)((M + 127) / 128) * (N / 256) * L;
     const bool wide = (N % 256 == 0) && tiles256 >= sm_count(dev);
-    // CTA-pair kernel: measured equal to the single-CTA kernel at 8192^3 (both end up power-capped), so it is
-    // opt-in: NVFP4_GEMM_PAIR=1 forces it wherever it applies, =2 lets pair_kernel_suits() decide.
-    static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 0; }();
+    // CTA-pair kernel (256 x 256 tiles on two SMs): a third fewer bytes per SM and K step; 192-196 us against 224 us
+    // at 8192^3.  Used wherever pair_kernel_suits() says so; NVFP4_GEMM_PAIR=0 turns it off, =1 forces it wherever
+    // the shape allows it at all.
+    static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 2; }();
     const bool use_pair = pair_mode != 0 && N % 256 == 0 && M >= 256 &&
                           (pair_mode == 1 || pair_kernel_suits(M, N, K, L, false, dev));
     // few tiles and a long K loop: split K across a cluster (NVFP4_GEMM_SPLITK=0 turns it off)
@@ -461,7 +454,7 @@ extern "C" int nvfp4_dual_gemm(const void* a, const void* b1, const void* b2, co
     p.budget_ns = wait_budget_ns();
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N / 128) * L;
-    static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 0; }();
+    static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 2; }();
     if (pair_mode != 0 && M >= 256 && (pair_mode == 1 || pair_kernel_suits(M, N, K, L, true, dev)))
         return launch_gemm_pair(true, ta, tb1, tb2, p, (cudaStream_t)stream);
     return launch_gemm<128, true, false, 4>(ta, tb1, tb2, p, (cudaStream_t)stream);

@@ -110,8 +110,8 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 const uint32_t sSFA = sB + SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
                 const int k0 = (kfirst + it) * BK;
                 mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
-                tma_load_3d(sA, &tmap_a, k0 >> p.kshift, m0, l, full);
-                tma_load_3d(sB, &tmap_b, k0 >> p.kshift, n0, l, full);
+                tma_load_3d(sA, &tmap_a, k0, m0, l, full);
+                tma_load_3d(sB, &tmap_b, k0, n0, l, full);
                 const size_t koff = (size_t)(k0 / 64) * 512;
                 bulk_g2s(sSFA, sfa_t + koff, 2048u, full);
                 bulk_g2s(sSFB, sfb_t + koff, 2048u, full);
@@ -246,9 +246,7 @@ int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
     attr.val.clusterDim.x = S; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    GemmParams q = p;
-    q.kshift = operand_kshift();
-    e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<S>, ta, tb, q);
+    e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<S>, ta, tb, p);
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
 

@@ -101,19 +101,21 @@ def format_report(data: dict, mode: str, task: str, system: dict | None = None) 
     if system:
         lines += ["", "Running on: " + ", ".join(f"{k} `{v}`" for k, v in system.items())]
     if data["benchmarks"]:
-        lines += ["", "| case | mean us | err us | best us | worst us | runs | floor us | mean / floor | status |",
-                  "|---|---|---|---|---|---|---|---|---|"]
+        lines += ["", "| case | mean us | err us | best us | worst us | runs | kernel us | floor us | mean / floor | kernel / floor | status |",
+                  "|---|---|---|---|---|---|---|---|---|---|---|"]
         for i, b in sorted(data["benchmarks"].items()):
             try:
                 mean, err, best, worst = (float(b[f]) / 1e3 for f in ("mean", "err", "best", "worst"))
+                kern = float(b["kernel_us"]) if "kernel_us" in b else None
                 try:
                     fl = floor_us(task, _spec_args(b.get("spec", "")))
-                    tail = f"{fl:.1f} | {mean / fl:.2f}"
+                    tail = f"{fl:.1f} | {mean / fl:.2f} | " + (f"{kern / fl:.2f}" if kern is not None else "-")
                 except Exception:
-                    tail = "- | -"
-                row = f"{mean:.1f} | {err:.2f} | {best:.1f} | {worst:.1f} | {b.get('runs', '-')} | {tail}"
+                    tail = "- | - | -"
+                row = (f"{mean:.1f} | {err:.2f} | {best:.1f} | {worst:.1f} | {b.get('runs', '-')} | "
+                       + (f"{kern:.1f}" if kern is not None else "-") + f" | {tail}")
             except (KeyError, ValueError):
-                row = "- | - | - | - | - | - | -"
+                row = "- | - | - | - | - | - | - | - | -"
             status = "fail: " + b.get("error", "failed") if b.get("status") == "fail" or "error" in b else "ok"
             lines.append(f"| `{b.get('spec', i)}` | {row} | {status} |")
     elif data["tests"]:

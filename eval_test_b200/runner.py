@@ -1,7 +1,7 @@
 """Local runner for the harness's shape-list files, in place of the remote launcher.
 
     python -m eval_test_b200.runner test        nvfp4_gemm  tests.txt
-    python -m eval_test_b200.runner benchmark   nvfp4_gemv  benchmarks.txt [--report]
+    python -m eval_test_b200.runner benchmark   nvfp4_gemv  benchmarks.txt [--report] [--kernel-time]
     python -m eval_test_b200.runner leaderboard nvfp4_dual_gemm benchmarks.txt
     python -m eval_test_b200.runner profile     nvfp4_gemm  benchmarks.txt
     python -m eval_test_b200.runner benchmark   nvfp4_gemm  benchmarks.txt --eval-dir <eval/> --submission <eval/nvfp4_gemm/submission.py>
@@ -298,7 +298,29 @@ def _benchmark(t: Task, args, flush, recheck, max_repeats, max_time_ns):
         return None, f"{type(e).__name__}: {e}"
 
 
-def run_benchmarks(t: Task, cases, log: Logger, leaderboard: bool = False) -> bool:
+def kernel_only_us(t: Task, args: dict, flush) -> float | None:
+    """Device time of the kernels of ONE call, cold L2, from the profiler's kernel records (no launch latency, no
+    host time): what remains of a sample once everything but the GPU work is taken away."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    data = t.generate_input(**args)
+    for _ in range(3):
+        t.kernel(data)
+    torch.cuda.synchronize()
+    best = None
+    for _ in range(5):
+        flush()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            t.kernel(data)
+            torch.cuda.synchronize()
+        us = sum(e.device_time_total for e in prof.key_averages() if "memset" not in e.key.lower())
+        if us > 0:
+            best = us if best is None else min(best, us)
+    return best
+
+
+def run_benchmarks(t: Task, cases, log: Logger, leaderboard: bool = False, kernel_time: bool = False) -> bool:
     flush = L2Flusher()
     ok_all = True
     if leaderboard:      # warm every shape up, then sample with the output re-checked on every repeat
@@ -313,6 +335,13 @@ def run_benchmarks(t: Task, cases, log: Logger, leaderboard: bool = False) -> bo
         if stats is not None:
             for f in fields(Stats):
                 log.log(f"benchmark.{i}.{f.name}", getattr(stats, f.name))
+        if kernel_time:
+            try:
+                us = kernel_only_us(t, case.args, flush)
+                if us is not None:
+                    log.log(f"benchmark.{i}.kernel_us", us)
+            except Exception as e:
+                log.log(f"benchmark.{i}.kernel_us_error", f"{type(e).__name__}: {e}")
         if error is not None or stats is None:
             ok_all = False
             log.log(f"benchmark.{i}.status", "fail")
@@ -348,6 +377,8 @@ def main(argv=None) -> int:
     ap.add_argument("--eval-dir", help="take generate_input / check_implementation from <eval-dir>/<task>/reference.py")
     ap.add_argument("--submission", help="time the custom_kernel of this submission.py instead of the library's")
     ap.add_argument("--report", action="store_true", help="print a markdown summary of the log at the end")
+    ap.add_argument("--kernel-time", action="store_true",
+                    help="benchmark modes: also log the kernels' own device time of one call (profiler records)")
     try:
         a = ap.parse_args(argv)
     except SystemExit:
@@ -366,7 +397,7 @@ def main(argv=None) -> int:
     elif a.mode == "profile":
         ok = run_profile(t, cases, log)
     else:
-        ok = run_benchmarks(t, cases, log, leaderboard=a.mode == "leaderboard")
+        ok = run_benchmarks(t, cases, log, leaderboard=a.mode == "leaderboard", kernel_time=a.kernel_time)
     if a.report:
         from . import report
         print(report.format_report(report.parse_log("\n".join(log.lines)), a.mode, a.task, report.system_info()))

@@ -56,6 +56,15 @@ def test_gemm_reference_style_bit_exact(oracle, m, n, k, l):
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
 
 
+def test_gemm_wide_single_cta_tiles_bit_exact(oracle):
+    """M = 640 is not a multiple of 256, so the CTA-pair kernel is not chosen; 5 x 32 tiles of 128 x 256 fill the
+    machine, so the single-CTA kernel runs with its 256-column tiles."""
+    from eval_test_b200 import inputs
+    data = to_device(inputs.gemm_reference_style(640, 8192, 512, 1, seed=12, device="cpu"))
+    got, want = _gemm(data), oracle.c_gemm(*gemm_oracle_args(data))
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
 @pytest.mark.parametrize("m,n,k,l,alpha", [(128, 256, 512, 1, 1.0), (200, 384, 768, 2, 0.5), (1000, 1280, 1024, 1, 0.5)])
 def test_gemm_quantized_within_tolerance(oracle, m, n, k, l, alpha):
     """N(0,1) data through the quantiser (the first case is the CPU-runnable configuration), ragged M,
@@ -181,7 +190,8 @@ print("pair ok")
 
 
 def test_cta_pair_kernels_in_a_child_process():
-    """The cta_group::2 variants (opt-in through NVFP4_GEMM_PAIR=1, read once per process): one pair tile, ragged
+    """The cta_group::2 variants forced onto small shapes (NVFP4_GEMM_PAIR=1, read once per process; by default
+    they are taken only when there are enough 256-row tiles to fill the machine): one pair tile, ragged
     M (the second CTA of the last row tile owns no rows), batches, several tiles per pair; GEMM bit-exact, dual
     GEMM within the harness's tolerance."""
     import os
