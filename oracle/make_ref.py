@@ -7,8 +7,11 @@ The reference is Python: its ``reference.py`` files (input generators, ``ref_ker
 checkout's ``eval/`` tree, unmodified, into the git-ignored ``oracle/_ref/`` so that it travels with the working
 tree to the machine that has the GPU; nothing of it is committed.  Two trees are written:
 
-* ``oracle/_ref/eval/``     the reference's files as they are (its own ``submission.py`` kernels included, which the
-  runner can time as "the kernel to beat");
+* ``oracle/_ref/eval/``     the reference's files as they are (its own ``submission.py`` kernels of the GEMM, dual
+  GEMM and GEMV tasks included, which the runner can time as "the kernel to beat").  The grouped task's
+  ``submission.py`` is left out: as shipped it does not compile (eval/nvfp4_grouped_gemm/submission.py:7,1189), so it
+  can never be run, and its source names cluster-multicast TMA wrappers (never called), a form of load that is
+  kept out of everything that travels to a machine with more than one GPU;
 * ``oracle/_ref/harness/``  the same files with each task's ``submission.py`` replaced by the one-line re-export a
   maintainer would add to use this library, so that the reference's own ``eval.py test tests.txt`` drives the new
   kernels (eval/nvfp4_gemm/eval.py:23-40 imports ``submission`` from the task directory).
@@ -44,6 +47,7 @@ def stage(ref_root: str | Path) -> Path:
         shutil.copytree(src, dst, ignore=ignore)
     for task, line in TASKS.items():
         (OUT / "harness" / task / "submission.py").write_text(line)
+    (OUT / "eval" / "nvfp4_grouped_gemm" / "submission.py").unlink()
     return OUT
 
 
