@@ -28,6 +28,16 @@ struct alignas(64) GroupEntry {
     int tiles_m, tiles_n;
 };
 
+// One problem of a grouped GEMM as the CTA-pair kernel sees it: its tiles are 256 x 256, the B map has 128-row
+// boxes (each CTA of a pair keeps half a B tile) and the scales come through tensor maps too.
+struct alignas(64) PairGroupEntry {
+    CUtensorMap ta, tb, tsa, tsb;
+    __half* c;            // [M][N]
+    int M, N, K;
+    int tile_start;       // index of this group's first pair tile in the launch-wide tile order
+    int tiles_m, tiles_n; // ceil(M / 256), N / 256
+};
+
 // Fused all-gather of an N-sharded GEMM: every output chunk is stored into the full C buffer of every rank (peer
 // memory mapped into this process, plain stores).  d[w] = byte distance of rank w's buffer from buffer 0.
 struct GatherOut {
@@ -60,6 +70,7 @@ struct GemmParams {
     int* status;
     unsigned long long budget_ns;
     const GroupEntry* table;  // grouped GEMM only: G entries, empty groups left out
+    const void* pair_table = nullptr;  // grouped GEMM on CTA pairs: G PairGroupEntry
     int G;
     int total_tiles;
 #ifdef NVFP4_PROFILE
@@ -306,6 +317,10 @@ int make_scale_tmap(CUtensorMap* map, const void* base, long atoms);
 bool pair_kernel_suits(int M, int N, int K, int L, bool dual, int dev);
 int launch_gemm_pair(bool dual, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                      cudaStream_t stream);
+// Grouped GEMM on CTA pairs: p.pair_table (device), p.G entries, p.total_tiles pair tiles.  max_pairs_grouped():
+// pairs that can be resident on the device (<= 0: the kernel cannot run there).
+int launch_gemm_pair_grouped(const GemmParams& p, cudaStream_t stream);
+int max_pairs_grouped(int dev);
 
 // Cluster split-K kernel for few-tile, long-K shapes (gemm_splitk_sm100.cu).  splitk_factor() returns the cluster
 // size (2, 4, 8) or 0 when the persistent kernel should be used; maps with 128-row boxes.

@@ -21,6 +21,11 @@
 //   * both CTAs' epilogue warps drain their own 128 accumulator rows and arrive on the LEADER's "drained" barriers.
 // The dual GEMM fits naturally: the leader keeps the B1 tile, the peer the B2 tile, the pair produces 256 x 128
 // outputs of silu(A.B1) * (A.B2).
+// GROUPED: the pair tiles of all groups form one launch-wide list (PairGroupEntry table in device memory, binary
+// search tile -> group, row tile fastest inside a group); every group has its own four tensor maps.  An expert layer
+// with M_g around 128 is bound by streaming the weights: with one pair per 256 columns of a group every weight byte
+// is fetched from HBM by exactly one CTA and every tile is a streaming tile, where the single-CTA kernel alternates
+// between a streaming tile (first 128 rows) and an MMA-bound one (rows 128..M_g-1, weights from L2).
 // Every mbarrier wait is bounded; the two hardware cluster barriers (after set-up, before exit) are reached by
 // every thread on every path.
 #include <cuda.h>
@@ -42,9 +47,68 @@ constexpr uint32_t PAIR_SFB_BYTES = 2 * 4 * 512;   // scales of all 256 B rows
 constexpr uint32_t PAIR_STAGE_BYTES = PAIR_A_BYTES + PAIR_B_BYTES + PAIR_SFA_BYTES + PAIR_SFB_BYTES;
 constexpr size_t PAIR_SMEM = PAIR_STAGES * PAIR_STAGE_BYTES + 1024;
 
-// Pair tile t -> batch, 256-row tile, column tile; same banded order as the single-CTA kernel.
+// Everything a role of one CTA needs to know about one pair tile.
+struct PairTile {
+    const CUtensorMap *ta, *tb, *tb2, *tsa, *tsb, *tsb2;
+    __half* c;            // output of this problem / batch, [M][N]
+    int M, N, kiters, l;
+    int m0;               // first row of THIS CTA's 128 rows
+    int n0;               // first output column of the pair tile
+    int atom_a, atom_b;   // scale atoms (512 bytes) of this CTA's A rows / of the tile's first 128 B rows at k = 0
+    int apb;              // atoms of one 128-row scale block = K / 64
+    bool a_rows_exist, peer_rows_exist;
+};
+
+// Pair tile t -> problem, batch, 256-row tile, column tile.  Plain / dual GEMM: the banded order of the single-CTA
+// kernel.  GROUPED: binary search of the group whose tile range holds t.
 // GEMM: column tile = 256 output columns.  DUAL: 128 output columns.
-template <bool DUAL>
+template <bool DUAL, bool GROUPED>
+__device__ __forceinline__ PairTile locate_pair(int t, const GemmParams& p, uint32_t rank, const CUtensorMap* ta,
+                                                const CUtensorMap* tb, const CUtensorMap* tb2, const CUtensorMap* tsa,
+                                                const CUtensorMap* tsb, const CUtensorMap* tsb2) {
+    constexpr int BN = DUAL ? 128 : 256;
+    PairTile ti;
+    int mt;
+    if (GROUPED) {
+        const PairGroupEntry* tab = reinterpret_cast<const PairGroupEntry*>(p.pair_table);
+        int lo = 0, hi = p.G - 1;
+        while (lo < hi) {
+            const int mid = (lo + hi + 1) >> 1;
+            if (__ldg(&tab[mid].tile_start) <= t) lo = mid; else hi = mid - 1;
+        }
+        const PairGroupEntry* e = tab + lo;
+        const int r = t - __ldg(&e->tile_start);
+        const int tiles_m = __ldg(&e->tiles_m);
+        const int nt = r / tiles_m;
+        mt = r - nt * tiles_m;
+        ti.ta = &e->ta; ti.tb = &e->tb; ti.tb2 = &e->tb; ti.tsa = &e->tsa; ti.tsb = &e->tsb; ti.tsb2 = &e->tsb;
+        ti.M = __ldg(&e->M); ti.N = __ldg(&e->N);
+        const int K = __ldg(&e->K);
+        ti.kiters = K / BK; ti.apb = K / 64; ti.l = 0;
+        ti.n0 = nt * BN;
+        ti.c = e->c;
+        ti.m0 = mt * 256 + (int)rank * 128;
+        ti.atom_a = (ti.m0 >> 7) * ti.apb;
+        ti.atom_b = (ti.n0 / 128) * ti.apb;
+    } else {
+        const int tiles_m = (p.M + 255) / 256, tiles_n = p.N / BN;
+        const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
+        const int RA = (p.M + 127) / 128, RB = p.N / 128;
+        mt = tc.mt;
+        ti.ta = ta; ti.tb = tb; ti.tb2 = tb2; ti.tsa = tsa; ti.tsb = tsb; ti.tsb2 = tsb2;
+        ti.M = p.M; ti.N = p.N; ti.kiters = p.K / BK; ti.apb = p.K / 64; ti.l = tc.l;
+        ti.n0 = tc.nt * BN;
+        ti.c = p.c + (size_t)tc.l * p.M * p.N;
+        ti.m0 = mt * 256 + (int)rank * 128;
+        ti.atom_a = (tc.l * RA + (ti.m0 >> 7)) * ti.apb;
+        ti.atom_b = (tc.l * RB + ti.n0 / 128) * ti.apb;
+    }
+    ti.a_rows_exist = ti.m0 < ti.M;
+    ti.peer_rows_exist = mt * 256 + 128 < ti.M;
+    return ti;
+}
+
+template <bool DUAL, bool GROUPED = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_b2, const __grid_constant__ CUtensorMap tmap_sfa,
@@ -82,13 +146,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         }
         mbar_init(ovl_free, 8);
         fence_mbar_init();
-        prefetch_tmap(&tmap_a);
-        prefetch_tmap(&tmap_b);
-        prefetch_tmap(&tmap_sfa);
-        prefetch_tmap(&tmap_sfb);
-        if (DUAL) {
-            prefetch_tmap(&tmap_b2);
-            prefetch_tmap(&tmap_sfb2);
+        if (!GROUPED) {
+            prefetch_tmap(&tmap_a);
+            prefetch_tmap(&tmap_b);
+            prefetch_tmap(&tmap_sfa);
+            prefetch_tmap(&tmap_sfb);
+            if (DUAL) {
+                prefetch_tmap(&tmap_b2);
+                prefetch_tmap(&tmap_sfb2);
+            }
         }
     }
     if (warp == 1) {
@@ -101,12 +167,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
-    const int tiles_m = (p.M + 255) / 256, tiles_n = p.N / BN;
-    const int total_tiles = tiles_m * tiles_n * p.L;
+    const int total_tiles = p.total_tiles;               // pair tiles of the launch
     const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
-    const int kiters = p.K / BK;
-    const int RA = (p.M + 127) / 128, RB = p.N / 128;
-    const int atoms_per_block = p.K / 64;                // scale atoms (512 bytes) of one 128-row block
+#define LOCATE_PAIR(t) locate_pair<DUAL, GROUPED>(t, p, rank, &tmap_a, &tmap_b, &tmap_b2, &tmap_sfa, &tmap_sfb, &tmap_sfb2)
 
     if (warp == 0) {
         // ------------------------------------------------------------------ producer (both CTAs, own tiles)
@@ -115,14 +178,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             bool alive = true;
             const uint32_t leader_full0 = mapa_shared(full0, 0);
             for (int t = pair; alive && t < total_tiles; t += npairs) {
-                const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-                const int m0 = tc.mt * 256 + (int)rank * 128;     // this CTA's A rows
-                const int n0 = tc.nt * BN;
-                const bool a_rows_exist = m0 < p.M;
-                const bool peer_rows_exist = tc.mt * 256 + 128 < p.M;
-                const int atom_a = (tc.l * RA + (m0 >> 7)) * atoms_per_block;
-                const int atom_b = (tc.l * RB + n0 / 128) * atoms_per_block;
-                for (int kit = 0; kit < kiters; kit++, it++) {
+                const PairTile ti = LOCATE_PAIR(t);
+                for (int kit = 0; kit < ti.kiters; kit++, it++) {
                     const int slot = it % STAGES;
                     if (!mbar_wait_cluster(empty0 + 8 * slot, ((it / STAGES) & 1) ^ 1, p.budget_ns)) {
                         report_status(p.status, DEV_TIMEOUT_PRODUCER);
@@ -140,18 +197,18 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     // tile) read as zeros; their scale block does not exist and is not fetched
                     if (rank == 0)
                         mbar_arrive_expect_tx(full0 + 8 * slot, 2u * (PAIR_A_BYTES + PAIR_B_BYTES + PAIR_SFB_BYTES) +
-                                                                    PAIR_SFA_BYTES + (peer_rows_exist ? PAIR_SFA_BYTES : 0u));
-                    tma_load_3d_pair(sA, &tmap_a, k0, m0, tc.l, full);
-                    if (a_rows_exist) tma_load_2d_pair(sSFA, &tmap_sfa, 0, atom_a + ka, full);
+                                                                    PAIR_SFA_BYTES + (ti.peer_rows_exist ? PAIR_SFA_BYTES : 0u));
+                    tma_load_3d_pair(sA, ti.ta, k0, ti.m0, ti.l, full);
+                    if (ti.a_rows_exist) tma_load_2d_pair(sSFA, ti.tsa, 0, ti.atom_a + ka, full);
                     if (DUAL) {
                         // leader keeps the B1 tile, peer the B2 tile; both need both scale blocks
-                        tma_load_3d_pair(sB, rank == 0 ? &tmap_b : &tmap_b2, k0, n0, tc.l, full);
-                        tma_load_2d_pair(sSFB, &tmap_sfb, 0, atom_b + ka, full);
-                        tma_load_2d_pair(sSFB + 2048u, &tmap_sfb2, 0, atom_b + ka, full);
+                        tma_load_3d_pair(sB, rank == 0 ? ti.tb : ti.tb2, k0, ti.n0, ti.l, full);
+                        tma_load_2d_pair(sSFB, ti.tsb, 0, ti.atom_b + ka, full);
+                        tma_load_2d_pair(sSFB + 2048u, ti.tsb2, 0, ti.atom_b + ka, full);
                     } else {
-                        tma_load_3d_pair(sB, &tmap_b, k0, n0 + (int)rank * 128, tc.l, full);
-                        tma_load_2d_pair(sSFB, &tmap_sfb, 0, atom_b + ka, full);
-                        tma_load_2d_pair(sSFB + 2048u, &tmap_sfb, 0, atom_b + atoms_per_block + ka, full);
+                        tma_load_3d_pair(sB, ti.tb, k0, ti.n0 + (int)rank * 128, ti.l, full);
+                        tma_load_2d_pair(sSFB, ti.tsb, 0, ti.atom_b + ka, full);
+                        tma_load_2d_pair(sSFB + 2048u, ti.tsb, 0, ti.atom_b + ti.apb + ka, full);
                     }
                 }
             }
@@ -182,6 +239,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     }
                     tc_fence_after_sync();
                     const uint32_t t_acc = tmem_base + buf * ACC1_OFF;
+                    const int kiters = LOCATE_PAIR(t).kiters;
                     for (int kit = 0; kit < kiters; kit++, it++) {
                         const int slot = it % STAGES;
                         const uint32_t par = (it / STAGES) & 1;
@@ -233,9 +291,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         const uint32_t l_acc_empty0 = mapa_shared(acc_empty0, 0), l_ovl_free = mapa_shared(ovl_free, 0);
         uint32_t tile_it = 0;
         for (int t = pair; t < total_tiles; t += npairs, tile_it++) {
-            const TileCoord tc = tile_coord(t, tiles_m, tiles_n);
-            const int row = tc.mt * 256 + (int)rank * 128 + q * 32 + lane;
-            const int n0 = tc.nt * BN;
+            const PairTile ti = LOCATE_PAIR(t);
+            const int row = ti.m0 + q * 32 + lane;
+            const int n0 = ti.n0;
             const uint32_t buf = tile_it & 1;
             if (!mbar_wait(acc_full0 + 8 * buf, (tile_it >> 1) & 1, p.budget_ns)) {
                 if (lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
@@ -243,19 +301,20 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             }
             tc_fence_after_sync();
             const uint32_t t_lane = tmem_base + buf * ACC1_OFF + ((uint32_t)(q * 32) << 16);
-            __half* crow = p.c + ((size_t)tc.l * p.M + (size_t)(row < p.M ? row : 0)) * p.N + n0;
+            __half* crow = ti.c + (size_t)(row < ti.M ? row : 0) * ti.N + n0;
             // the shared columns are released through the leader's barrier by a cluster-scope arrive
             if (buf == 0)
-                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS, true>(t_lane, crow, row < p.M, n0, p.N, p.alpha,
+                epilogue_tile<BN, DUAL, int(ACC1_OFF) / 32, OV_CHUNKS, true>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha,
                                                                             l_ovl_free, lane);
             else
-                epilogue_tile<BN, DUAL, 0, OV_CHUNKS, true>(t_lane, crow, row < p.M, n0, p.N, p.alpha, l_ovl_free, lane);
+                epilogue_tile<BN, DUAL, 0, OV_CHUNKS, true>(t_lane, crow, row < ti.M, n0, ti.N, p.alpha, l_ovl_free, lane);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster_relaxed(l_acc_empty0 + 8 * buf);   // accumulator read out (see ovl_free)
         }
     }
 
+#undef LOCATE_PAIR
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();   // neither CTA frees tensor memory or exits while the other may still touch it
@@ -268,23 +327,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
 // ------------------------------------------------------------------------------------------ host side
 namespace {
 
-template <bool DUAL>
+template <bool DUAL, bool GROUPED>
 int configure(int dev) {
     static bool done[64] = {};
     if (done[dev]) return NVFP4_OK;
-    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(gemm_pair_kernel<DUAL, GROUPED>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)PAIR_SMEM);
     if (e != cudaSuccess) return (int)e;
     done[dev] = true;
     return NVFP4_OK;
 }
 
-template <bool DUAL>
+template <bool DUAL, bool GROUPED>
 int max_pairs(int dev) {
     static int cached[64] = {};
     if (cached[dev]) return cached[dev];
     // the occupancy query fails for more dynamic shared memory than the kernel has been allowed so far
-    if (configure<DUAL>(dev) != NVFP4_OK) return -1;
+    if (configure<DUAL, GROUPED>(dev) != NVFP4_OK) return -1;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * sm_count(dev));
     cfg.blockDim = dim3(GEMM_THREADS);
@@ -295,7 +354,7 @@ int max_pairs(int dev) {
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<DUAL>, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<DUAL, GROUPED>, &cfg) != cudaSuccess || n <= 0) {
         cudaGetLastError();
         n = 0;
     }
@@ -303,18 +362,18 @@ int max_pairs(int dev) {
     return cached[dev];
 }
 
-template <bool DUAL>
-int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
-           cudaStream_t stream) {
+// tiles: pair tiles of the launch; the maps are the plain / dual GEMM's (ignored by the grouped kernel).
+template <bool DUAL, bool GROUPED>
+int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const CUtensorMap& tsa,
+           const CUtensorMap& tsb, const CUtensorMap& tsb2, const GemmParams& p, int tiles, cudaStream_t stream) {
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
-    int rc = configure<DUAL>(dev);
+    int rc = configure<DUAL, GROUPED>(dev);
     if (rc) return rc;
-    const int pairs_max = max_pairs<DUAL>(dev);
+    const int pairs_max = max_pairs<DUAL, GROUPED>(dev);
     if (pairs_max <= 0) return NVFP4_ERR_UNSUPPORTED;
-    const int tiles = ((p.M + 255) / 256) * (p.N / (DUAL ? 128 : 256)) * p.L;
     if (tiles <= 0) return NVFP4_OK;
     const int pairs = tiles < pairs_max ? tiles : pairs_max;
     cudaLaunchConfig_t cfg = {};
@@ -327,9 +386,19 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
     attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
+    GemmParams q = p;
+    q.total_tiles = tiles;
+    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<DUAL, GROUPED>, ta, tb, tb2, tsa, tsb, tsb2, q);
+    return e == cudaSuccess ? NVFP4_OK : (int)e;
+}
+
+template <bool DUAL>
+int launch_plain(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
+                 cudaStream_t stream) {
+    const int tiles = ((p.M + 255) / 256) * (p.N / (DUAL ? 128 : 256)) * p.L;
     const long ka = p.K / 64;
     CUtensorMap tsa, tsb, tsb2;
-    rc = make_scale_tmap(&tsa, p.sfa, (long)p.L * ((p.M + 127) / 128) * ka);
+    int rc = make_scale_tmap(&tsa, p.sfa, (long)p.L * ((p.M + 127) / 128) * ka);
     if (rc) return rc;
     rc = make_scale_tmap(&tsb, p.sfb, (long)p.L * (p.N / 128) * ka);
     if (rc) return rc;
@@ -338,15 +407,14 @@ int launch(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
         rc = make_scale_tmap(&tsb2, p.sfb2, (long)p.L * (p.N / 128) * ka);
         if (rc) return rc;
     }
-    e = cudaLaunchKernelEx(&cfg, gemm_pair_kernel<DUAL>, ta, tb, tb2, tsa, tsb, tsb2, p);
-    return e == cudaSuccess ? NVFP4_OK : (int)e;
+    return launch<DUAL, false>(ta, tb, tb2, tsa, tsb, tsb2, p, tiles, stream);
 }
 
 }  // namespace
 
 bool pair_kernel_suits(int M, int N, int K, int L, bool dual, int dev) {
     if (M < 256 || N % (dual ? 128 : 256) != 0 || dev >= 64) return false;
-    const int pairs = dual ? max_pairs<true>(dev) : max_pairs<false>(dev);
+    const int pairs = dual ? max_pairs<true, false>(dev) : max_pairs<false, false>(dev);
     if (pairs <= 0) return false;
     const long tiles = (long)((M + 255) / 256) * (N / (dual ? 128 : 256)) * L;
     // rows of the last 256-row tile that do not exist are wasted work for one CTA of the pair
@@ -356,7 +424,15 @@ bool pair_kernel_suits(int M, int N, int K, int L, bool dual, int dev) {
 
 int launch_gemm_pair(bool dual, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
                      cudaStream_t stream) {
-    return dual ? launch<true>(ta, tb, tb2, p, stream) : launch<false>(ta, tb, tb2, p, stream);
+    return dual ? launch_plain<true>(ta, tb, tb2, p, stream) : launch_plain<false>(ta, tb, tb2, p, stream);
+}
+
+int max_pairs_grouped(int dev) { return dev < 64 ? max_pairs<false, true>(dev) : -1; }
+
+int launch_gemm_pair_grouped(const GemmParams& p, cudaStream_t stream) {
+    // the kernel takes its maps from the table; the six map parameters only have to be valid objects
+    static const CUtensorMap dummy = {};
+    return launch<false, true>(dummy, dummy, dummy, dummy, dummy, dummy, p, p.total_tiles, stream);
 }
 
 }  // namespace nvfp4

@@ -577,9 +577,9 @@ namespace {
 // launches of the earlier streams.
 constexpr int TABLE_SLOTS = 8;
 struct TableSlot {
-    GroupEntry* host = nullptr;
-    GroupEntry* dev = nullptr;
-    int capacity = 0;
+    unsigned char* host = nullptr;   // GroupEntry[] or PairGroupEntry[]
+    unsigned char* dev = nullptr;
+    size_t capacity = 0;             // bytes
     cudaEvent_t done = nullptr;      // after the latest launch that reads this table (and, transitively, all earlier ones)
     cudaEvent_t uploaded = nullptr;  // after the host-to-device copy of the table
     cudaStream_t last_stream = nullptr;  // stream of the latest upload or launch
@@ -587,7 +587,7 @@ struct TableSlot {
     // the call this slot's device table was built for: an identical call (same pointers and sizes, the usual
     // case when a layer runs again) reuses the table without re-encoding or uploading anything
     std::vector<nvfp4_group_t> key;
-    int live = 0, tiles = 0, bn = 0;
+    int live = 0, tiles = 0, bn = 0;   // bn: tile width of the single-CTA kernel (128 / 256), or 2 = CTA pairs
 };
 struct TableRing {
     TableSlot slots[TABLE_SLOTS];
@@ -596,7 +596,7 @@ struct TableRing {
 std::mutex g_table_mu;
 TableRing g_rings[64];
 
-int acquire_slot(int dev, int G, TableSlot** out) {
+int acquire_slot(int dev, size_t bytes, TableSlot** out) {
     TableRing& ring = g_rings[dev];
     TableSlot& s = ring.slots[ring.next];
     ring.next = (ring.next + 1) % TABLE_SLOTS;
@@ -615,15 +615,15 @@ int acquire_slot(int dev, int G, TableSlot** out) {
         if (e != cudaSuccess) return (int)e;
     }
     s.used = false;
-    if (s.capacity < G) {
-        int cap = 64;
-        while (cap < G) cap *= 2;
+    if (s.capacity < bytes) {
+        size_t cap = 32 * 1024;
+        while (cap < bytes) cap *= 2;
         if (s.host) cudaFreeHost(s.host);
         if (s.dev) cudaFree(s.dev);
         s.host = nullptr; s.dev = nullptr; s.capacity = 0;
-        e = cudaHostAlloc((void**)&s.host, sizeof(GroupEntry) * cap, cudaHostAllocDefault);
+        e = cudaHostAlloc((void**)&s.host, cap, cudaHostAllocDefault);
         if (e != cudaSuccess) return (int)e;
-        e = cudaMalloc((void**)&s.dev, sizeof(GroupEntry) * cap);
+        e = cudaMalloc((void**)&s.dev, cap);
         if (e != cudaSuccess) return (int)e;
         s.capacity = cap;
     }
@@ -634,12 +634,27 @@ int acquire_slot(int dev, int G, TableSlot** out) {
 }  // namespace
 }  // namespace nvfp4
 
+// Launch on a slot's finished table.  kind: 128 / 256 = tile width of the single-CTA kernel, 2 = CTA pairs.
+static int launch_grouped(const TableSlot& slot, GemmParams& p, cudaStream_t st) {
+    p.G = slot.live; p.total_tiles = slot.tiles;
+    if (slot.bn == 2) {
+        p.table = nullptr; p.pair_table = slot.dev;
+        return launch_gemm_pair_grouped(p, st);
+    }
+    p.table = reinterpret_cast<const GroupEntry*>(slot.dev); p.pair_table = nullptr;
+    const CUtensorMap& dm = reinterpret_cast<const GroupEntry*>(slot.host)[0].ta;
+    return slot.bn == 256 ? launch_gemm<256, false, true, 4>(dm, dm, dm, p, st)
+                          : launch_gemm<128, false, true, 6>(dm, dm, dm, p, st);
+}
+
 extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alpha, void* stream) {
     if (!groups) return NVFP4_ERR_NULL;
     if (G <= 0) return NVFP4_ERR_SHAPE;
     if (G > 65536) return NVFP4_ERR_TOO_MANY_GROUPS;
     bool wide = true;
     int live = 0;
+    long pair_tiles = 0;
+    double work_pair = 0, work_single = 0;   // padded rows x N x K: what the tensor pipe is asked to do
     for (int g = 0; g < G; g++) {
         const nvfp4_group_t& q = groups[g];
         if (q.M < 0 || q.N <= 0 || q.K <= 0) return NVFP4_ERR_SHAPE;
@@ -654,13 +669,22 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
         if ((uintptr_t)q.c & 31) return NVFP4_ERR_ALIGN;
         if (q.N % 256 != 0) wide = false;
         live++;
+        pair_tiles += (long)((q.M + 255) / 256) * (q.N / 256);
+        work_pair += (double)((q.M + 255) / 256 * 256) * q.N * q.K;
+        work_single += (double)((q.M + 127) / 128 * 128) * q.N * q.K;
     }
     if (live == 0) return NVFP4_OK;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
-    const int bn = wide ? 256 : 128;
+    // CTA pairs (256 x 256 tiles): when every N allows it, there is at least one tile per pair of SMs and the rows
+    // padded up to 256 do not cost more than half again the tensor work (an expert layer with M_g around 128 is bound
+    // by streaming the weights, which pairs do best).  NVFP4_GEMM_PAIR=0 turns them off, =1 forces them.
+    static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 2; }();
+    const bool use_pair = wide && pair_mode != 0 && max_pairs_grouped(dev) > 0 &&
+                          (pair_mode == 1 || (pair_tiles >= max_pairs_grouped(dev) && work_pair <= 1.5 * work_single));
+    const int bn = use_pair ? 2 : (wide ? 256 : 128);
 
     std::lock_guard<std::mutex> lk(g_table_mu);
     cudaStream_t st = (cudaStream_t)stream;
@@ -684,10 +708,7 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
             e = cudaStreamWaitEvent(st, slot->uploaded, 0);
             if (e != cudaSuccess) return (int)e;
         }
-        p.table = slot->dev; p.G = slot->live; p.total_tiles = slot->tiles;
-        const CUtensorMap& dm = slot->host[0].ta;
-        int rc2 = slot->bn == 256 ? launch_gemm<256, false, true, 4>(dm, dm, dm, p, st)
-                                  : launch_gemm<128, false, true, 6>(dm, dm, dm, p, st);
+        int rc2 = launch_grouped(*slot, p, st);
         if (other_stream) {
             // `done` is about to move to this stream: first make this stream's record wait for the launches the
             // old record stood for, so that the slot is not rewritten while any of them still reads the table
@@ -699,13 +720,31 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
         if (rc2) return rc2;
         return e == cudaSuccess ? NVFP4_OK : (int)e;
     }
-    int rc = acquire_slot(dev, live, &slot);
+    const size_t entry_bytes = use_pair ? sizeof(PairGroupEntry) : sizeof(GroupEntry);
+    int rc = acquire_slot(dev, entry_bytes * live, &slot);
     if (rc) return rc;
     int tiles = 0, n = 0;
     for (int g = 0; g < G; g++) {
         const nvfp4_group_t& q = groups[g];
         if (q.M == 0) continue;
-        GroupEntry& en = slot->host[n++];
+        if (use_pair) {
+            PairGroupEntry& en = reinterpret_cast<PairGroupEntry*>(slot->host)[n++];
+            rc = make_operand_tmap(&en.ta, q.a, q.M, q.K, 1, 128);
+            if (rc) return rc;
+            rc = make_operand_tmap(&en.tb, q.b, q.N, q.K, 1, 128);
+            if (rc) return rc;
+            rc = make_scale_tmap(&en.tsa, q.sfa_sw, (long)((q.M + 127) / 128) * (q.K / 64));
+            if (rc) return rc;
+            rc = make_scale_tmap(&en.tsb, q.sfb_sw, (long)(q.N / 128) * (q.K / 64));
+            if (rc) return rc;
+            en.c = (__half*)q.c;
+            en.M = q.M; en.N = q.N; en.K = q.K;
+            en.tiles_m = (q.M + 255) / 256; en.tiles_n = q.N / 256;
+            en.tile_start = tiles;
+            tiles += en.tiles_m * en.tiles_n;
+            continue;
+        }
+        GroupEntry& en = reinterpret_cast<GroupEntry*>(slot->host)[n++];
         rc = make_operand_tmap(&en.ta, q.a, q.M, q.K, 1, 128);
         if (rc) return rc;
         rc = make_operand_tmap(&en.tb, q.b, q.N, q.K, 1, bn);
@@ -716,17 +755,14 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
         en.tile_start = tiles;
         tiles += en.tiles_m * en.tiles_n;
     }
-    e = cudaMemcpyAsync(slot->dev, slot->host, sizeof(GroupEntry) * live, cudaMemcpyHostToDevice, st);
+    e = cudaMemcpyAsync(slot->dev, slot->host, entry_bytes * live, cudaMemcpyHostToDevice, st);
     if (e != cudaSuccess) return (int)e;
     e = cudaEventRecord(slot->uploaded, st);
     if (e != cudaSuccess) return (int)e;
     slot->last_stream = st;
-    p.table = slot->dev; p.G = live; p.total_tiles = tiles;
     slot->key.assign(groups, groups + G);
     slot->live = live; slot->tiles = tiles; slot->bn = bn;
-    const CUtensorMap& dummy = slot->host[0].ta;
-    rc = wide ? launch_gemm<256, false, true, 4>(dummy, dummy, dummy, p, st)
-              : launch_gemm<128, false, true, 6>(dummy, dummy, dummy, p, st);
+    rc = launch_grouped(*slot, p, st);
     slot->used = true;
     e = cudaEventRecord(slot->done, st);
     if (rc) return rc;

@@ -161,6 +161,52 @@ def test_grouped_repeated_calls_and_streams(oracle):
             assert np.array_equal(out_np(c)[0].view(np.uint16), w.view(np.uint16))
 
 
+_PAIR_CHILD = r'''
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from _util import grouped_oracle_args, out_np, to_device
+from eval_test_b200 import _lib, check, inputs, nvfp4_grouped_gemm
+from oracle import nvfp4_oracle as O
+cases = [([96, 128], [256, 256], [256, 512]),                    # one pair tile each, second CTA without rows / full
+         ([300, 0, 130, 512, 1], [256, 512, 256, 768, 256], [512, 256, 256, 256, 768]),   # ragged, empty, several row tiles
+         ([256, 257], [512, 256], [1024, 256])]
+for m, n, k in cases:
+    d = to_device(inputs.grouped_gemm_reference_style(m, n, k, len(m), seed=41, device="cpu"))
+    outs = nvfp4_grouped_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    for got, want in zip(outs, O.c_grouped_gemm(grouped_oracle_args(d))):
+        assert np.array_equal(out_np(got)[0].view(np.uint16), want.view(np.uint16)), (m, n, k)
+    outs = nvfp4_grouped_gemm.custom_kernel(d)                   # the same call again: reused table
+    torch.cuda.synchronize()
+    for got, want in zip(outs, O.c_grouped_gemm(grouped_oracle_args(d))):
+        assert np.array_equal(out_np(got)[0].view(np.uint16), want.view(np.uint16)), (m, n, k)
+d = to_device(inputs.grouped_gemm_quantized([140, 100, 0, 260], [512] * 4, [768] * 4, 4, seed=42, device="cpu"))
+outs = nvfp4_grouped_gemm.custom_kernel(d, alpha=0.5)
+torch.cuda.synchronize()
+for got, want in zip(outs, O.c_grouped_gemm(grouped_oracle_args(d), alpha=0.5)):
+    if want.size:
+        assert check.verbose_allclose(torch.from_numpy(out_np(got)[0]), torch.from_numpy(want), rtol=1e-3, atol=1e-3) == []
+print("grouped pair ok")
+'''
+
+
+def test_grouped_on_cta_pairs_in_a_child_process():
+    """The CTA-pair kernel under the grouped scheduler, forced onto small problems (NVFP4_GEMM_PAIR=1, read once per
+    process; by default it is taken when the layer has at least one 256 x 256 tile per pair of SMs, as the full-size
+    expert-layer test above does): groups of one pair tile whose second CTA owns no rows, ragged and empty groups,
+    several row tiles, a repeated call; dyadic inputs bit-exact, quantised inputs within the harness's tolerance."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, NVFP4_GEMM_PAIR="1")
+    res = subprocess.run([sys.executable, "-c", _PAIR_CHILD, root], env=env, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0 and "grouped pair ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
 def test_grouped_bad_arguments():
     import ctypes
     from eval_test_b200 import _lib
