@@ -71,6 +71,9 @@ struct GemmParams {
     unsigned long long budget_ns;
     const GroupEntry* table;  // grouped GEMM only: G entries, empty groups left out
     const void* pair_table = nullptr;  // grouped GEMM on CTA pairs: G PairGroupEntry
+    float* sk_scratch = nullptr;       // stream-K: one partial accumulator (2 CTAs x 128 rows x 256 fp32) per pair
+    unsigned int* sk_flags = nullptr;  // stream-K: [pair][8 epilogue warps of the pair] = epoch once the partial is written
+    unsigned int sk_epoch = 0;
     int G;
     int total_tiles;
 #ifdef NVFP4_PROFILE
@@ -199,14 +202,18 @@ __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32]
         if (!half) return;
         __syncwarp();
         const GatherOut& g = *gc->g;
+        // Four lanes cover one row's 128 bytes with a 32-byte piece each (whole sectors: 16-byte pieces leave
+        // half-written sectors behind, which is slow in local memory and worse over NVLink); one store instruction
+        // writes 8 rows x 128 contiguous bytes.
 #pragma unroll
-        for (int it = 0; it < 8; it++) {
-            const int r = it * 4 + (lane >> 3), pc = lane & 7;
-            const uint4 val = st[r * 8 + (pc ^ (r & 7))];
+        for (int it = 0; it < 4; it++) {
+            const int r = it * 8 + (lane >> 2), pc = (lane & 3) * 2;
+            const uint4 v0 = st[r * 8 + (pc ^ (r & 7))], v1 = st[r * 8 + ((pc + 1) ^ (r & 7))];
             if (pred && r < gc->rows) {
                 // dst is this (odd) chunk's column; the pair starts 32 columns = 64 bytes before it
                 char* q0 = reinterpret_cast<char*>(dst) - 64 + (size_t)r * g.ldc * 2 + pc * 16;
-                for (int k = 0; k < g.n; k++) *reinterpret_cast<uint4*>(q0 + g.d[k]) = val;   // every rank's buffer
+                const uint32_t w8[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+                for (int k = 0; k < g.n; k++) st_global_256(q0 + g.d[k], w8);   // every rank's buffer
             }
         }
         __syncwarp();
@@ -255,6 +262,49 @@ __device__ __forceinline__ void store_chunk_q(QuantOut& q, int cc, const uint32_
     }
 }
 
+// Stream-K: when the tiles of a launch do not fill the last round of the machine, the K steps of all tiles form one
+// list and every CTA (pair) takes a contiguous share of it, so a tile may be computed by two or more of them.  A
+// share that ends inside a tile leaves its fp32 partial accumulator in a scratch slot of its own (mode 1); the
+// share that holds the tile's last K step adds the partials in ascending K order to its own accumulator and writes
+// the output (mode 2).  A thread owns one accumulator row: `out` / `in[j]` point at that row's 256 floats.
+struct SkEpi {
+    float* out = nullptr;
+    const float* in[8] = {};
+    int n_in = 0;
+};
+
+// 32 accumulator values of this thread's row -> scratch (whole 32-byte sectors).
+__device__ __forceinline__ void sk_store_chunk(float* dst, const uint32_t (&v)[32]) {
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const uint32_t w8[8] = {v[8 * j], v[8 * j + 1], v[8 * j + 2], v[8 * j + 3],
+                                v[8 * j + 4], v[8 * j + 5], v[8 * j + 6], v[8 * j + 7]};
+        st_global_256(dst + 8 * j, w8);
+    }
+}
+
+// s = (in[0] + in[1]) + ... for 32 columns of this thread's row: the partial sums in the order of their K ranges
+// (issued before the accumulator chunk is waited for, so that the two latencies overlap).
+__device__ __forceinline__ void sk_load_chunk(float (&s)[32], const SkEpi& sk, int col) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const float4 t = __ldcg(reinterpret_cast<const float4*>(sk.in[0] + col) + i);
+        s[4 * i] = t.x; s[4 * i + 1] = t.y; s[4 * i + 2] = t.z; s[4 * i + 3] = t.w;
+    }
+    for (int j = 1; j < sk.n_in; j++) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const float4 t = __ldcg(reinterpret_cast<const float4*>(sk.in[j] + col) + i);
+            s[4 * i] += t.x; s[4 * i + 1] += t.y; s[4 * i + 2] += t.z; s[4 * i + 3] += t.w;
+        }
+    }
+}
+// out = s + own: the finishing share's own K range comes last.
+__device__ __forceinline__ void sk_add_chunk(uint32_t (&out)[32], const uint32_t (&own)[32], const float (&s)[32]) {
+#pragma unroll
+    for (int i = 0; i < 32; i++) out[i] = __float_as_uint(s[i] + __uint_as_float(own[i]));
+}
+
 // Epilogue of one tile for one warp (its 32 accumulator rows).  C0 is the first 32-column chunk, relative to
 // the accumulator base, that this buffer shares with the other one (OVC chunks; OVC = 0: nothing shared).
 // The shared chunks are pulled into registers first and released at once, so the next tile's MMAs wait only
@@ -262,10 +312,12 @@ __device__ __forceinline__ void store_chunk_q(QuantOut& q, int cc, const uint32_
 // CLUSTER: ovl_free is a shared::cluster address (the barrier may live in the peer CTA).
 // QOUT: NVFP4 output through q instead of fp16 through crow.
 // GATHER: fp16 output to every rank's buffer (crow: the warp's first row in buffer 0, see store_chunk).
-template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false, bool GATHER = false>
+// SK: 0 = whole tile; 1 = stream-K partial out (all BN columns as fp32 to sk->out; use BN = 256, DUAL = false);
+//     2 = stream-K finish (sk->in partials added before the normal epilogue).
+template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false, bool GATHER = false, int SK = 0>
 __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, bool row_ok, int n0, int N, float alpha,
                                               uint32_t ovl_free, int lane, QuantOut* q = nullptr,
-                                              const GatherCtx* gc = nullptr) {
+                                              const GatherCtx* gc = nullptr, const SkEpi* sk = nullptr) {
     constexpr int NCH = BN / 32;
     uint32_t ov[OVC > 0 ? OVC : 1][32];
     if (OVC > 0) {
@@ -287,11 +339,30 @@ __device__ __forceinline__ void epilogue_tile(uint32_t t_lane, __half* crow, boo
         uint32_t v[32], w[32];
         const bool v_pre = OVC > 0 && cc >= C0 && cc < C0 + OVC;
         const bool w_pre = DUAL && OVC > 0 && cc + YOFF >= C0 && cc + YOFF < C0 + OVC;
+        float sx[SK == 2 ? 32 : 1], sy[(SK == 2 && DUAL) ? 32 : 1];
+        if (SK == 2) {
+            sk_load_chunk(reinterpret_cast<float(&)[32]>(sx), *sk, cc * 32);
+            if (DUAL) sk_load_chunk(reinterpret_cast<float(&)[32]>(sy), *sk, (cc + YOFF) * 32);
+        }
         if (!v_pre) tc_ld_32x32(t_lane + cc * 32, v);
         if (DUAL && !w_pre) tc_ld_32x32(t_lane + (cc + YOFF) * 32, w);
         if (!v_pre || (DUAL && !w_pre)) tc_wait_ld();
         const bool pred = (GATHER || row_ok) && n0 + cc * 32 < N;
         // (index clamps only keep the never-taken branch in range for the compiler)
+        if (SK == 1) {
+            sk_store_chunk(sk->out + cc * 32, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v);
+            continue;
+        }
+        if (SK == 2) {
+            uint32_t vs[32], ws[32];
+            sk_add_chunk(vs, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
+                         reinterpret_cast<const float(&)[32]>(sx));
+            if (DUAL)
+                sk_add_chunk(ws, w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w,
+                             reinterpret_cast<const float(&)[32]>(sy));
+            store_chunk<DUAL, false>(crow + cc * 32, vs, ws, alpha, pred);
+            continue;
+        }
         if (QOUT)
             store_chunk_q<DUAL>(*q, cc, v_pre ? ov[(cc - C0) < 0 || (cc - C0) >= OVC ? 0 : cc - C0] : v,
                                 w_pre ? ov[(cc + YOFF - C0) < 0 || (cc + YOFF - C0) >= OVC ? 0 : cc + YOFF - C0] : w, alpha,

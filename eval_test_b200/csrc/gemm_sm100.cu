@@ -653,8 +653,6 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     if (G > 65536) return NVFP4_ERR_TOO_MANY_GROUPS;
     bool wide = true;
     int live = 0;
-    long pair_tiles = 0;
-    double work_pair = 0, work_single = 0;   // padded rows x N x K: what the tensor pipe is asked to do
     for (int g = 0; g < G; g++) {
         const nvfp4_group_t& q = groups[g];
         if (q.M < 0 || q.N <= 0 || q.K <= 0) return NVFP4_ERR_SHAPE;
@@ -669,21 +667,18 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
         if ((uintptr_t)q.c & 31) return NVFP4_ERR_ALIGN;
         if (q.N % 256 != 0) wide = false;
         live++;
-        pair_tiles += (long)((q.M + 255) / 256) * (q.N / 256);
-        work_pair += (double)((q.M + 255) / 256 * 256) * q.N * q.K;
-        work_single += (double)((q.M + 127) / 128 * 128) * q.N * q.K;
     }
     if (live == 0) return NVFP4_OK;
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
-    // CTA pairs (256 x 256 tiles): when every N allows it, there is at least one tile per pair of SMs and the rows
-    // padded up to 256 do not cost more than half again the tensor work (an expert layer with M_g around 128 is bound
-    // by streaming the weights, which pairs do best).  NVFP4_GEMM_PAIR=0 turns them off, =1 forces them.
+    // CTA pairs (256 x 256 tiles, gemm_pair_kernel<false, true>) are opt-in here (NVFP4_GEMM_PAIR=1): on the expert
+    // layer of 64 groups with M_g around 128 they measured 234.7 us against 214.2 us for the single-CTA kernel.  The
+    // layer streams its weights from HBM; a pair advances only when BOTH CTAs' halves of a stage have arrived, and
+    // every group with M_g <= 128 leaves the second CTA's tensor work wasted.
     static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 2; }();
-    const bool use_pair = wide && pair_mode != 0 && max_pairs_grouped(dev) > 0 &&
-                          (pair_mode == 1 || (pair_tiles >= max_pairs_grouped(dev) && work_pair <= 1.5 * work_single));
+    const bool use_pair = wide && pair_mode == 1 && max_pairs_grouped(dev) > 0;
     const int bn = use_pair ? 2 : (wide ? 256 : 128);
 
     std::lock_guard<std::mutex> lk(g_table_mu);
@@ -773,6 +768,7 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
 // device tables, events) and the status words.  The caller must have synchronised the streams it used.
 namespace nvfp4 {
 void free_status_words();
+void free_stream_k_scratch();
 }
 extern "C" int nvfp4_shutdown(void) {
     std::lock_guard<std::mutex> lk(g_table_mu);
@@ -793,6 +789,7 @@ extern "C" int nvfp4_shutdown(void) {
         g_rings[dev].next = 0;
     }
     cudaSetDevice(cur);
+    free_stream_k_scratch();
     free_status_words();
     return NVFP4_OK;
 }

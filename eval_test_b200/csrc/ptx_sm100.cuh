@@ -88,6 +88,16 @@ __device__ __forceinline__ void report_status(int* status, int code) {
     if (status) atomicCAS_system(status, 0, code);
 }
 
+// Flags in global memory between CTAs of one launch (device scope).
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const unsigned int* p) {
+    uint32_t v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(unsigned int* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
 // ------------------------------------------------------------------ async-proxy copies
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

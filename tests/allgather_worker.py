@@ -24,6 +24,23 @@ def main():
     out.wait_all()
     torch.cuda.synchronize()
     assert torch.equal(out.view().view(torch.int16), want.view(torch.int16)), "gemm copy differs"
+    # The whole protocol, three rounds into the SAME buffers with different operands: launch, wait_all, a reader on the
+    # stream (a checksum of this rank's copy), release, next launch.  Without release() a rank that is ahead would
+    # overwrite a copy whose reader has not run yet; nothing synchronises the host between the rounds.
+    rounds, sums = [], []
+    for seed in (21, 22, 23):
+        d = inputs.gemm_quantized(m, n, k, l, seed=seed, device=dev)
+        rounds.append((shard.shard_gemm(d, rank, world), nvfp4_gemm.custom_kernel(d, alpha=0.5).view(torch.int16).clone()))
+    torch.cuda.synchronize()
+    dist.barrier()
+    for sh, _ in rounds:
+        shard.gemm_allgather(sh, out, rank, alpha=0.5)
+        out.wait_all()
+        sums.append(out.view().view(torch.int16).to(torch.int64).sum())     # the reader, stream-ordered
+        out.release()
+    torch.cuda.synchronize()
+    for (_, ref), got in zip(rounds, sums):
+        assert int(got) == int(ref.to(torch.int64).sum()), "a copy was overwritten before its reader ran"
     fd = inputs.dual_gemm_quantized(m, n, k, 1, seed=10, device=dev)
     wantd = nvfp4_dual_gemm.custom_kernel(fd).clone()
     outd = shard.GatheredOutput(m, n, 1, dev)

@@ -204,6 +204,70 @@ def test_cta_pair_kernels_in_a_child_process():
     assert res.returncode == 0 and "pair ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
 
 
+_STREAMK_CHILD = r'''
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from _util import dual_oracle_args, gemm_oracle_args, out_np, to_device
+from eval_test_b200 import _lib, check, inputs, nvfp4_dual_gemm, nvfp4_gemm
+from oracle import nvfp4_oracle as O
+# pair tiles on 74 pairs: 128 tiles of 8 K steps (shares of 13.8 steps: every tile whole or cut in two), 40 tiles of
+# 16 steps (shares of 8.6: every tile cut into two or three pieces; ragged M: the last row tile's second CTA owns no
+# rows), 48 tiles of 16 steps in two batches
+for (m, n, k, l) in [(2048, 4096, 2048, 1), (1100, 2048, 4096, 1), (768, 2048, 4096, 2)]:
+    d = to_device(inputs.gemm_reference_style(m, n, k, l, seed=51, device="cpu"))
+    nvfp4_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    assert np.array_equal(out_np(d[-1]).view(np.uint16), O.c_gemm(*gemm_oracle_args(d)).view(np.uint16)), (m, n, k, l)
+    nvfp4_gemm.custom_kernel(d)            # again: the flags of the first launch must not satisfy the second
+    torch.cuda.synchronize()
+    assert np.array_equal(out_np(d[-1]).view(np.uint16), O.c_gemm(*gemm_oracle_args(d)).view(np.uint16)), (m, n, k, l)
+d = to_device(inputs.gemm_quantized(1024, 2304, 2048, 1, seed=52, device="cpu"))
+nvfp4_gemm.custom_kernel(d, alpha=0.5)
+torch.cuda.synchronize()
+got, want = torch.from_numpy(out_np(d[-1])), torch.from_numpy(O.c_gemm(*gemm_oracle_args(d), 0.5))
+assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+for (m, n, k, l) in [(1024, 1792, 1024, 1), (768, 1920, 4096, 1)]:
+    d = to_device(inputs.dual_gemm_reference_style(m, n, k, l, seed=53, device="cpu"))
+    nvfp4_dual_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    got, want = out_np(d[-1]).astype(np.float32), O.c_dual_gemm(*dual_oracle_args(d)).astype(np.float32)
+    assert np.all(np.abs(got - want) <= 1e-3 + 1e-3 * np.abs(want)), (m, n, k, l)
+print("streamk ok")
+'''
+
+
+def test_stream_k_on_cta_pairs_in_a_child_process():
+    """The stream-K schedule of the CTA-pair kernel (opt-in: NVFP4_GEMM_STREAMK=1, with NVFP4_GEMM_PAIR=1, read once
+    per process) on shapes whose tiles do not fill the last round of pairs: tiles cut into two and into several
+    pieces, ragged M, batches, the same call twice (a new epoch of the flags); dyadic inputs must match the oracle bit
+    for bit whatever the order in which the partial sums are added; quantised and dual-GEMM inputs within the
+    harness's tolerance."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, NVFP4_GEMM_PAIR="1", NVFP4_GEMM_STREAMK="1")
+    res = subprocess.run([sys.executable, "-c", _STREAMK_CHILD, root], env=env, capture_output=True, text=True,
+                         timeout=600)
+    assert res.returncode == 0 and "streamk ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_column_shard_of_the_large_gemm_against_scaled_mm():
+    """M = 8192, N = 1024, K = 8192 (one eighth of the large GEMM's columns, what a rank of an 8-GPU run computes:
+    128 pair tiles for 74 pairs of SMs, a partly filled second round): every element against torch._scaled_mm."""
+    from eval_test_b200 import check, inputs, nvfp4_gemm, reference_check
+    data = inputs.gemm_quantized(8192, 1024, 8192, 1, seed=3, device="cuda")
+    got = nvfp4_gemm.custom_kernel(data, alpha=1.0).clone()
+    _status_ok()
+    want = reference_check.ref_gemm(data)
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
 _SPLITK_CHILD = r'''
 import sys
 import numpy as np, torch

@@ -193,10 +193,9 @@ print("grouped pair ok")
 
 
 def test_grouped_on_cta_pairs_in_a_child_process():
-    """The CTA-pair kernel under the grouped scheduler, forced onto small problems (NVFP4_GEMM_PAIR=1, read once per
-    process; by default it is taken when the layer has at least one 256 x 256 tile per pair of SMs, as the full-size
-    expert-layer test above does): groups of one pair tile whose second CTA owns no rows, ragged and empty groups,
-    several row tiles, a repeated call; dyadic inputs bit-exact, quantised inputs within the harness's tolerance."""
+    """The CTA-pair kernel under the grouped scheduler (opt-in: NVFP4_GEMM_PAIR=1, read once per process): groups of
+    one pair tile whose second CTA owns no rows, ragged and empty groups, several row tiles, a repeated call; dyadic
+    inputs bit-exact, quantised inputs within the harness's tolerance."""
     import os
     import subprocess
     import sys
