@@ -122,8 +122,7 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int tiles_m, int tiles_n)
 __device__ __forceinline__ float silu_mul(float x, float y) { return __fdividef(x, 1.0f + __expf(-x)) * y; }
 
 // Tile t of a plain / dual GEMM (all batches share the maps; the batch is the third TMA coordinate) or of a
-// grouped GEMM (binary search of the group whose tile range holds t; row-tile index fastest inside a group,
-// so the tiles that share a B column-tile run together and B streams from HBM once).
+// grouped GEMM (binary search of the group whose tile range holds t; column tile fastest inside a group).
 template <int BN, bool DUAL, bool GROUPED>
 __device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUtensorMap* ta, const CUtensorMap* tb,
                                            const CUtensorMap* tb2) {
@@ -136,9 +135,14 @@ __device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUt
             if (__ldg(&p.table[mid].tile_start) <= t) lo = mid; else hi = mid - 1;
         }
         const GroupEntry* e = p.table + lo;
+        // Column tile fastest inside a group: first every column tile of the first 128 rows, then of the next 128, ...
+        // The row tiles of one column tile still run within one round of CTAs of each other, so the weights come from
+        // HBM once.  (With the row tile fastest and an even number of tiles in every group, CTAs with an even index
+        // got every first-row tile - the ones that stream the weights from HBM, about twice as long - and the odd ones
+        // the cheap remainder tiles: half the machine idled at the end of an expert layer.)
         const int r = t - __ldg(&e->tile_start);
-        const int tiles_m = __ldg(&e->tiles_m);
-        const int nt = r / tiles_m, mt = r - nt * tiles_m;
+        const int tiles_n = __ldg(&e->tiles_n);
+        const int mt = r / tiles_n, nt = r - mt * tiles_n;
         ti.ta = &e->ta; ti.tb = &e->tb; ti.tb2 = &e->tb;
         ti.M = __ldg(&e->M); ti.N = __ldg(&e->N);
         const int K = __ldg(&e->K);

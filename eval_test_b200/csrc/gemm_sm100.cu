@@ -688,6 +688,9 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     p.M = p.N = p.K = 0; p.L = 1; p.alpha = alpha;
     p.status = status_word(dev);
     p.budget_ns = wait_budget_ns();
+#ifdef NVFP4_PROFILE
+    { const char* e_ = getenv("NVFP4_PROF_PTR"); p.prof = e_ ? (unsigned long long*)strtoull(e_, nullptr, 0) : nullptr; }
+#endif
     TableSlot* slot = nullptr;
     for (TableSlot& cand : g_rings[dev].slots) {
         if (cand.used && cand.key.size() == (size_t)G &&
