@@ -56,6 +56,25 @@ def test_gemm_reference_style_bit_exact(oracle, m, n, k, l):
     assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
 
 
+@pytest.mark.parametrize("m,n,k,l", [(2176, 2560, 1024, 1), (2048, 2304, 512, 2), (4096, 2048, 256, 1)])
+def test_gemm_cta_pairs_by_default_bit_exact(oracle, m, n, k, l):
+    """Shapes with at least one 256 x 256 tile per pair of SMs take the CTA-pair kernel by default: a ragged last row
+    tile (M = 8.5 x 256: its second CTA owns no rows), batches, a single K step per tile."""
+    from eval_test_b200 import inputs
+    data = to_device(inputs.gemm_reference_style(m, n, k, l, seed=61, device="cpu"))
+    got, want = _gemm(data), oracle.c_gemm(*gemm_oracle_args(data))
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
+@pytest.mark.parametrize("m,n,k,l", [(2304, 1280, 512, 1), (2176, 640, 256, 2)])
+def test_dual_gemm_cta_pairs_by_default(oracle, m, n, k, l):
+    from eval_test_b200 import check, inputs
+    data = to_device(inputs.dual_gemm_reference_style(m, n, k, l, seed=62, device="cpu"))
+    got = torch.from_numpy(_dual(data))
+    want = torch.from_numpy(oracle.c_dual_gemm(*dual_oracle_args(data)))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+
+
 def test_gemm_wide_single_cta_tiles_bit_exact(oracle):
     """M = 640 is not a multiple of 256, so the CTA-pair kernel is not chosen; 5 x 32 tiles of 128 x 256 fill the
     machine, so the single-CTA kernel runs with its 256-column tiles."""
