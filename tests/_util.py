@@ -1,9 +1,7 @@
 """Helpers shared by the tests: turn the harness's input tuples into the plain arrays the CPU oracle takes."""
 from __future__ import annotations
 
-import numpy as np
 import torch
-
 
 from eval_test_b200.hostviews import operand_np, out_np, scales_np  # noqa: F401  (re-exported for the tests)
 
