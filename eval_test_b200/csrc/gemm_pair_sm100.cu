@@ -360,13 +360,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const int row = ti.m0 + q * 32 + lane;
             const int n0 = ti.n0;
             const uint32_t buf = tile_it & 1;
-#ifdef NVFP4_EPI_SLEEP
-            // experiment: do not poll while the tile's MMAs cannot be finished yet
-            if (!mbar_try_wait(acc_full0 + 8 * buf, (tile_it >> 1) & 1)) {
-                const int ks = (STREAMK ? wk.k1 - wk.k0 : ti.kiters);
-                if (ks > 8) __nanosleep((ks - 8) * NVFP4_EPI_SLEEP);
-            }
-#endif
             if (!mbar_wait(acc_full0 + 8 * buf, (tile_it >> 1) & 1, p.budget_ns)) {
                 if (lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
                 break;
