@@ -2,14 +2,18 @@
 // benchmark list, eval/nvfp4_gemm/benchmarks.txt:1-3): split K across a thread-block CLUSTER.
 //
 // With M = 128 and N = 7168 there are 56 tiles of 128 x 128 for 148 SMs, each CTA walks 64 K steps one after the
-// other and a single CTA cannot pull more than about 100-180 GB/s through its four stages: a long K loop on a
+// other and a single CTA cannot pull more than about 100-180 GB/s through its stages: a long K loop on a
 // third of the machine.  Here the
 // S CTAs of a cluster (S = 2, 4 or 8) share ONE output tile: CTA r accumulates K steps [r*k/S, (r+1)*k/S) in its
 // own tensor memory, then the partial sums are reduced through distributed shared memory:
-//   * every CTA writes its fp32 partial tile (64 KB) to its own shared memory,
-//   * a cluster-scope mbarrier round tells every CTA that all partials are written,
-//   * CTA r reduces the column slice [r*128/S, (r+1)*128/S): each thread reads its row's slice from all S CTAs with
-//     ld.shared::cluster, adds them in rank order (deterministic), applies alpha, rounds to fp16 and stores.
+//   * CTA r owns the column slice [r*128/S, (r+1)*128/S) of the tile: it keeps its own partial sums of that slice
+//     in registers and writes the other slices of its fp32 partial tile to its own shared memory (over the stage
+//     ring, which is idle by then),
+//   * each warp tells the S-1 other CTAs (cluster-scope mbarrier) that its rows are written,
+//   * CTA r reads its slice of every peer's partial tile with ld.shared::cluster, adds the partials in a fixed order
+//     (its own, then ranks r+1, r+2, ... modulo S: deterministic), applies alpha, rounds to fp16 and stores.
+// The TMA producer starts loading before the rest of the CTA has finished its set-up: it needs only the barriers it
+// initialised itself.
 // No global scratch, no atomics.  One tile per cluster (the shapes this serves have fewer tiles than SMs).
 // Every mbarrier wait is bounded; the closing hardware cluster barrier is reached by every thread on every path.
 #include <cuda.h>
@@ -24,11 +28,16 @@
 namespace nvfp4 {
 
 constexpr int SK_BN = 128;
-constexpr int SK_STAGES = 4;
+// six stages of 36 KB: with a cold L2 (how the harness times a call) M=128 N=7168 K=16384 takes 21.3 us against
+// 23.8 us with four stages
+constexpr int SK_STAGES = 6;
 constexpr uint32_t SK_A_BYTES = 128 * 128, SK_B_BYTES = 128 * 128, SK_SF_BYTES = 2048;
 constexpr uint32_t SK_STAGE_BYTES = SK_A_BYTES + SK_B_BYTES + 2 * SK_SF_BYTES;
 constexpr uint32_t SK_RED_BYTES = 128 * SK_BN * 4;   // fp32 partial tile
-constexpr size_t SK_SMEM = SK_STAGES * SK_STAGE_BYTES + SK_RED_BYTES + 1024;
+// the partial tile reuses the stage ring: once "accumulator complete" has fired, every load has landed and every
+// MMA has read its stage
+static_assert(SK_STAGES * SK_STAGE_BYTES >= SK_RED_BYTES, "the partial tile lives in the stage ring");
+constexpr size_t SK_SMEM = SK_STAGES * SK_STAGE_BYTES + 1024;
 
 __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
     float4 v;
@@ -54,7 +63,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     __shared__ uint32_t tmem_base_slot;
 
     const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t red0 = smem0 + STAGES * SK_STAGE_BYTES;     // same offset in every CTA of the cluster
+    const uint32_t red0 = smem0;                               // same offset in every CTA of the cluster
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
@@ -62,25 +71,35 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const uint32_t red_ready = acc_full + 8;                   // 4 epilogue warps of each of the S CTAs
 
     if (threadIdx.x == 0) {
+        prefetch_tmap(&tmap_a);
+        prefetch_tmap(&tmap_b);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
         mbar_init(acc_full, 1);
-        mbar_init(red_ready, 4 * S);
+        mbar_init(red_ready, 4 * (S - 1));
         fence_mbar_init();
-        prefetch_tmap(&tmap_a);
-        prefetch_tmap(&tmap_b);
     }
     if (warp == 1) {
         tmem_alloc(smem_u32(&tmem_base_slot), TCOLS);
         tmem_relinquish();
     }
-    tc_fence_before_sync();
-    __syncthreads();
-    cluster_sync_all();     // every CTA's barriers exist before a peer arrives on them
-    tc_fence_after_sync();
-    const uint32_t tmem_base = tmem_base_slot;
+    // Peers arrive on this CTA's red_ready barrier only after their cluster_wait_acquire() below, i.e. after every
+    // thread here has arrived, thread 0 (which initialised the barrier) among them.  The producer warp arrives
+    // after it has issued its loads (a release-arrive takes about half a microsecond, and nobody needs it before
+    // this CTA's partial sums exist).
+    if (warp != 0) cluster_arrive_release();
+    uint32_t tmem_base = 0;
+    if (warp == 0) {
+        __syncwarp();                        // the loading lane sees the barriers lane 0 initialised
+        named_bar_arrive(1, GEMM_THREADS);   // ... and so will the other warps; this one does not wait for them
+    } else {
+        tc_fence_before_sync();
+        named_bar_sync(1, GEMM_THREADS);
+        tc_fence_after_sync();
+        tmem_base = tmem_base_slot;
+    }
 
     // tile of this cluster, K range of this CTA
     const int tiles_m = (p.M + BM - 1) / BM, tiles_n = p.N / SK_BN;
@@ -117,6 +136,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 bulk_g2s(sSFB, sfb_t + koff, 2048u, full);
             }
         }
+        __syncwarp();
+        cluster_arrive_release();
+        cluster_wait_acquire();
     } else if (warp == 1) {
         if (elect_one()) {
             constexpr uint32_t idesc = make_idesc_nvfp4(BM, SK_BN);
@@ -145,20 +167,26 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             }
             if (alive) tc_commit(acc_full);
         }
+        cluster_wait_acquire();
     } else {
         // ------------------------------------------------------------------ epilogue warps: partial -> smem -> reduce
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
+        constexpr int OWN_CHUNKS = SLICE >= 32 ? SLICE / 32 : 1;        // 32-column chunks that hold this CTA's slice
+        constexpr int PER_CHUNK = SLICE >= 32 ? 1 : 32 / SLICE;         // slices per chunk
+        const int own_chunk0 = (int)rank * OWN_CHUNKS / PER_CHUNK;
         bool ok = mbar_wait(acc_full, 0, p.budget_ns);
         if (!ok && lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
+        const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
         if (ok) {
             tc_fence_after_sync();
-            const uint32_t t_lane = tmem_base + ((uint32_t)(q * 32) << 16);
             // partial tile layout: 16-byte chunk c4 of row r at (c4 * 128 + r) * 16 -> consecutive lanes,
-            // consecutive addresses, for the writes here and for the (remote) reads below
+            // consecutive addresses, for the writes here and for the peers' reads below
             uint8_t* red_local = smem_raw + (red0 - smem_u32(smem_raw));
 #pragma unroll
             for (int cc = 0; cc < SK_BN / 32; cc++) {
+                // a chunk that holds nothing but this CTA's own slice stays in tensor memory
+                if (SLICE >= 32 && cc >= own_chunk0 && cc < own_chunk0 + OWN_CHUNKS) continue;
                 uint32_t v[32];
                 tc_ld_32x32(t_lane + cc * 32, v);
                 tc_wait_ld();
@@ -168,25 +196,46 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                         make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
         }
-        // tell every CTA of the cluster (this one included) that this warp's rows are written; a warp whose
-        // accumulator never completed still arrives, so that no peer waits for it in vain
+        // tell the other CTAs of the cluster that this warp's rows are written, one lane per peer (a release-arrive
+        // on a remote barrier takes hundreds of cycles, and one thread's arrives queue up behind one another); a
+        // warp whose accumulator never completed still arrives, so that no peer waits for it in vain
+        cluster_wait_acquire();     // the peers' barriers exist
         __syncwarp();
-        if (lane == 0) {
-#pragma unroll
-            for (int c = 0; c < S; c++) mbar_arrive_cluster(mapa_shared(red_ready, (uint32_t)c));
-        }
+        if (lane < S && lane != (int)rank) mbar_arrive_cluster(mapa_shared(red_ready, (uint32_t)lane));
+        float acc[SLICE];
         if (ok) {
+            // this CTA's own slice, while the peers' signals are on their way
+            if constexpr (SLICE >= 32) {
+#pragma unroll
+                for (int i = 0; i < OWN_CHUNKS; i++) {
+                    uint32_t v[32];
+                    tc_ld_32x32(t_lane + (own_chunk0 + i) * 32, v);
+                    tc_wait_ld();
+#pragma unroll
+                    for (int j = 0; j < 32; j++) acc[32 * i + j] = __uint_as_float(v[j]);
+                }
+            } else {
+                uint32_t v[32];
+                tc_ld_32x32(t_lane + own_chunk0 * 32, v);
+                tc_wait_ld();
+                const int part = (int)rank % PER_CHUNK;
+#pragma unroll
+                for (int j = 0; j < SLICE; j++) {
+                    float x = __uint_as_float(v[j]);
+#pragma unroll
+                    for (int h = 1; h < PER_CHUNK; h++)
+                        if (part == h) x = __uint_as_float(v[h * SLICE + j]);
+                    acc[j] = x;
+                }
+            }
             ok = mbar_wait_cluster(red_ready, 0, p.budget_ns);
             if (!ok && lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
         }
         if (ok) {
             const int row = m0 + row_in_tile;
-            float acc[SLICE];
 #pragma unroll
-            for (int i = 0; i < SLICE; i++) acc[i] = 0.f;
-#pragma unroll
-            for (int c = 0; c < S; c++) {
-                const uint32_t peer = mapa_shared(red0, (uint32_t)c);
+            for (int i = 1; i < S; i++) {
+                const uint32_t peer = mapa_shared(red0, (rank + (uint32_t)i) % (uint32_t)S);
 #pragma unroll
                 for (int j = 0; j < SLICE / 4; j++) {
                     const int c4 = (int)rank * (SLICE / 4) + j;
@@ -253,17 +302,19 @@ int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams
 }  // namespace
 
 // Cluster size to split K with, or 0 when the shape is better served by the persistent kernel.
-// Measured on B200 (device time per call, CUDA-graph replay): the reduction through distributed shared memory
-// costs about 3 us, a K step about 0.2 us, so splitting pays only for long K loops - M=128 N=7168 K=16384:
-// 16.4 us unsplit, 14.2 us with S=2; M=128 N=4096 K=7168: 9.6 / 9.5 / 9.4 us for S = 1 / 2 / 4; K=2048: 5.6 us
-// unsplit, 7.2 us with S=2.  Hence: at most half the SMs busy without splitting, and at least 16 K steps per CTA.
+// Measured on B200, device time of one call with a cold L2 (a 512 MiB fill before every call, which is how the
+// harness times): M=128 N=7168 K=16384 (56 tiles, 64 K steps) 25.3 us unsplit, 20.3 us with S=2, 30 us with S=4
+// (224 CTAs: two rounds); M=128 N=4096 K=7168 (32 tiles, 28 K steps) 11.8 us unsplit, 10.6 us with S=2, 10.1 us
+// with S=4; M=128 N=7168 K=2048 (8 K steps) 7.0 us unsplit, 8.0 us with S=2.  The reduction through distributed
+// shared memory costs about 2 us, a K step about 0.2 us.  Hence: all CTAs resident at once, at most half the SMs busy
+// without splitting, and at least 7 K steps per CTA.
 int splitk_factor(int M, int N, int K, int L, int dev) {
     const long tiles = (long)((M + BM - 1) / BM) * (N / SK_BN) * L;
     const int kiters = K / BK;
     const int sms = sm_count(dev);
     if (tiles <= 0 || tiles * 2 > sms) return 0;
     for (int s = 4; s >= 2; s /= 2)
-        if (tiles * s <= sms && kiters / s >= 16) return s;
+        if (tiles * s <= sms && kiters / s >= 7) return s;
     return 0;
 }
 

@@ -255,6 +255,22 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
 }
+// The two halves on their own: a CTA arrives as soon as its own barriers are initialised and waits only where it
+// first touches a peer's shared memory.  Every thread that arrives must wait before it arrives again.
+__device__ __forceinline__ void cluster_arrive_release() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait_acquire() {
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Named CTA barrier `id` for `count` threads (a multiple of 32): warps that only publish (the one that initialised
+// the mbarriers) arrive and go on, warps that consume what was published wait.
+__device__ __forceinline__ void named_bar_arrive(uint32_t id, uint32_t count) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
+__device__ __forceinline__ void named_bar_sync(uint32_t id, uint32_t count) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
+}
 // shared::cluster address of the same shared-memory location in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t rank) {
     uint32_t r;
