@@ -392,10 +392,8 @@ gemv_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                 // tell every CTA of the cluster (this one included) that this warp's rows are written; a warp whose
                 // accumulator never completed still arrives, so that no peer waits for it in vain
                 __syncwarp();
-                if (lane == 0) {
-#pragma unroll
-                    for (int c = 0; c < S; c++) mbar_arrive_cluster(mapa_shared(red_ready0 + 8 * buf, (uint32_t)c));
-                }
+                // (one lane per CTA: a thread's release-arrives on remote barriers queue up behind one another)
+                if (lane < S) mbar_arrive_cluster(mapa_shared(red_ready0 + 8 * buf, (uint32_t)lane));
                 if (!ok) break;
                 if (!mbar_wait_cluster(red_ready0 + 8 * buf, par, p.budget_ns)) {
                     if (lane == 0) report_status(p.status, DEV_TIMEOUT_EPILOGUE);
