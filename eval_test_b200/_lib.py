@@ -8,7 +8,9 @@ from pathlib import Path
 
 _PKG = Path(__file__).resolve().parent
 CSRC = _PKG / "csrc"
-SO_PATH = _PKG / "libnvfp4_b200.so"
+BUILT_SO = _PKG / "libnvfp4_b200.so"     # what build() makes
+# what load() opens: NVFP4_B200_LIB names another build of the library (an instrumented one, say)
+SO_PATH = Path(os.environ["NVFP4_B200_LIB"]).resolve() if os.environ.get("NVFP4_B200_LIB") else BUILT_SO
 HEADER = _PKG.parent / "include" / "nvfp4_b200.h"
 
 NVCC_FLAGS = [
@@ -22,9 +24,9 @@ def sources() -> list[Path]:
 
 
 def _stale() -> bool:
-    if not SO_PATH.exists():
+    if not BUILT_SO.exists():
         return True
-    t = SO_PATH.stat().st_mtime
+    t = BUILT_SO.stat().st_mtime
     deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + [HEADER]
     return any(d.stat().st_mtime > t for d in deps)
 
@@ -33,15 +35,15 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile every kernel for sm_100a into one shared library next to this file (nvcc cross-compiles
     without a GPU)."""
     if not force and not _stale():
-        return SO_PATH
+        return BUILT_SO
     nvcc = os.environ.get("NVCC", "nvcc")
-    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(SO_PATH), *map(str, sources())]
+    cmd = [nvcc, *NVCC_FLAGS, *(["-Xptxas", "-v"] if verbose else []), "-o", str(BUILT_SO), *map(str, sources())]
     res = subprocess.run(cmd, capture_output=True, text=True)
     if res.returncode != 0:
         raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
     if verbose:
         print(res.stderr)
-    return SO_PATH
+    return BUILT_SO
 
 
 class Group(ctypes.Structure):

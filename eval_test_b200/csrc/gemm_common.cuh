@@ -38,23 +38,47 @@ struct alignas(64) PairGroupEntry {
     int tiles_m, tiles_n; // ceil(M / 256), N / 256
 };
 
-// Fused all-gather of an N-sharded GEMM: every output chunk is stored into the full C buffer of every rank (peer
-// memory mapped into this process, plain stores).  d[w] = byte distance of rank w's buffer from buffer 0.
+// Fused all-gather of an N-sharded GEMM: every output tile is stored into the full C buffer of every rank (peer
+// memory mapped into this process) by asynchronous bulk tensor stores out of shared memory, one per rank, so that
+// the warps that drain the accumulators do not wait for NVLink.
+#ifndef NVFP4_GATHER_BOXES
+#define NVFP4_GATHER_BOXES 2
+#endif
+constexpr int GATHER_BOXES = NVFP4_GATHER_BOXES;   // 4 KB boxes per epilogue warp, filled in turn
+
 struct GatherOut {
     int n = 0;                  // ranks (0: not a gathering launch)
+#ifdef NVFP4_PROFILE
+    unsigned mask = 0xffu;      // ranks whose copy is actually stored (timing experiments)
+#endif
     int ldc = 0;                // row pitch of the full C in elements (N of all ranks together)
     int col0 = 0;               // first column of this rank's slice
-    long long d[8] = {};
-    __half* c0 = nullptr;       // buffer 0
 };
 
-// What one epilogue warp needs for a gathering store: the launch's description, 4 KB of shared memory of its own
-// and how many of its 32 rows exist.
+// One tensor map per rank over its full C, [L][M][ldc] fp16, box 64 columns x 32 rows, 128-byte swizzle: a kernel
+// parameter of the gathering instantiations only.
+struct GatherMaps { CUtensorMap m[8]; };
+struct NoGatherMaps { int unused; };
+template <bool GATHER> struct GatherMapsOf { using type = NoGatherMaps; };
+template <> struct GatherMapsOf<true> { using type = GatherMaps; };
+
+// What one epilogue warp needs for a gathering store: the maps, GATHER_BOXES x 4 KB of shared memory of its own (1024-byte
+// aligned; a box of 32 rows x 128 bytes each, filled in turn) and where its rows are in the full C.
 struct GatherCtx {
-    const GatherOut* g;
-    uint4* stage;      // 4 KB: 32 rows x 128 bytes
-    int rows;
-    int cc;            // chunk of the tile being stored
+    const CUtensorMap* maps;
+    int n;                 // ranks
+    uint4* stage;          // the warp's 8 KB ...
+    uint32_t stage_smem;   // ... and their shared-memory address
+    uint32_t uses;         // boxes filled so far by this warp (modulo GATHER_BOXES picks the box)
+    int x, y, z;           // the tile's first column in the full C, the warp's first row, the batch
+    bool rows_exist;       // the warp's first row is inside M (the store clips the rest)
+#ifdef NVFP4_PROFILE
+    unsigned mask;
+    __device__ bool enabled(int r) const { return (mask >> r) & 1u; }
+#else
+    __device__ bool enabled(int) const { return true; }
+#endif
+    int cc;                // chunk of the tile being stored
 };
 
 struct GemmParams {
@@ -174,9 +198,8 @@ __device__ __forceinline__ TileInfo locate(int t, const GemmParams& p, const CUt
 
 // fp32 accumulator chunk(s) -> 32 fp16 outputs of one row, written as two whole 32-byte sectors
 // (16-byte stores left half-written sectors behind and cost 35 us at 8192^3).
-// GATHER: dst is the warp's first row (the same pointer in every lane) in buffer 0 and pred only says that the
-// columns exist.  The warp's rows are turned through shared memory so that the pieces that cross NVLink are whole
-// 128-byte lines instead of 32 separate 32-byte pieces per instruction.
+// GATHER: dst is unused and pred only says that the columns exist; the warp's rows go through shared memory and
+// from there, as boxes of 32 rows x 128 bytes, into every rank's C (see GatherCtx).
 template <bool DUAL, bool GATHER = false>
 __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32], const uint32_t (&w)[32], float alpha,
                                             bool pred, const GatherCtx* gc = nullptr) {
@@ -194,33 +217,32 @@ __device__ __forceinline__ void store_chunk(__half* dst, const uint32_t (&v)[32]
         o[i] = *reinterpret_cast<uint32_t*>(&h);
     }
     if (GATHER) {
-        // Two chunks (128 bytes of every row) are collected in the warp's 4 KB before they go out: a store
-        // instruction then writes 4 rows x 128 contiguous bytes.  16-byte pieces are XOR-swizzled by the row so
-        // that both the row-wise writes and the transposed reads use every bank.
+        // Two chunks (128 bytes of every row) are collected in one of the warp's two 4 KB boxes, 16-byte pieces
+        // XOR-swizzled by the row exactly as the 128-byte swizzle of the tensor maps expects (and so that the
+        // row-wise writes use every bank); then one lane per rank issues the bulk tensor store of the box into that
+        // rank's C.  The stores run on their own: the warp goes back to the accumulator, and comes back to a box
+        // only after the stores that read it two boxes ago have done so.
+        GatherCtx& g = *const_cast<GatherCtx*>(gc);
         const int lane = threadIdx.x & 31;
-        uint4* st = gc->stage;
-        const int half = gc->cc & 1;
+        const int half = g.cc & 1;
+        const uint32_t b = g.uses % (uint32_t)GATHER_BOXES;
+        uint4* st = g.stage + b * 256;
+        if (!half && g.uses >= (uint32_t)GATHER_BOXES) {
+            if (lane < g.n) tma_store_wait_read<GATHER_BOXES - 1>();
+            __syncwarp();
+        }
 #pragma unroll
         for (int j = 0; j < 4; j++)
             st[lane * 8 + ((4 * half + j) ^ (lane & 7))] = make_uint4(o[4 * j], o[4 * j + 1], o[4 * j + 2], o[4 * j + 3]);
         if (!half) return;
+        fence_proxy_async_smem();   // the box was written by ordinary stores, the bulk store reads it as the async proxy
         __syncwarp();
-        const GatherOut& g = *gc->g;
-        // Four lanes cover one row's 128 bytes with a 32-byte piece each (whole sectors: 16-byte pieces leave
-        // half-written sectors behind, which is slow in local memory and worse over NVLink); one store instruction
-        // writes 8 rows x 128 contiguous bytes.
-#pragma unroll
-        for (int it = 0; it < 4; it++) {
-            const int r = it * 8 + (lane >> 2), pc = (lane & 3) * 2;
-            const uint4 v0 = st[r * 8 + (pc ^ (r & 7))], v1 = st[r * 8 + ((pc + 1) ^ (r & 7))];
-            if (pred && r < gc->rows) {
-                // dst is this (odd) chunk's column; the pair starts 32 columns = 64 bytes before it
-                char* q0 = reinterpret_cast<char*>(dst) - 64 + (size_t)r * g.ldc * 2 + pc * 16;
-                const uint32_t w8[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-                for (int k = 0; k < g.n; k++) st_global_256(q0 + g.d[k], w8);   // every rank's buffer
-            }
+        if (lane < g.n) {
+            if (pred && g.rows_exist && g.enabled(lane))
+                tma_store_3d(&g.maps[lane], g.stage_smem + b * 4096u, g.x + (g.cc >> 1) * 64, g.y, g.z);
+            tma_store_commit();      // (also when nothing was stored: the count of groups is what picks the box)
         }
-        __syncwarp();
+        g.uses++;
         return;
     }
     if (pred) {
@@ -315,7 +337,7 @@ __device__ __forceinline__ void sk_add_chunk(uint32_t (&out)[32], const uint32_t
 // for those loads, not for the conversion and stores.
 // CLUSTER: ovl_free is a shared::cluster address (the barrier may live in the peer CTA).
 // QOUT: NVFP4 output through q instead of fp16 through crow.
-// GATHER: fp16 output to every rank's buffer (crow: the warp's first row in buffer 0, see store_chunk).
+// GATHER: fp16 output to every rank's buffer (crow unused, see store_chunk and GatherCtx).
 // SK: 0 = whole tile; 1 = stream-K partial out (all BN columns as fp32 to sk->out; use BN = 256, DUAL = false);
 //     2 = stream-K finish (sk->in partials added before the normal epilogue).
 template <int BN, bool DUAL, int C0, int OVC, bool CLUSTER = false, bool QOUT = false, bool GATHER = false, int SK = 0>

@@ -42,7 +42,8 @@ namespace nvfp4 {
 template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false, bool GATHER = false>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-            const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmap_b2,
+            const __grid_constant__ typename GatherMapsOf<GATHER>::type gmaps, const GemmParams p) {
     constexpr int MMA_N = DUAL ? 2 * BN : BN;          // rows of the B tile in shared memory
     constexpr int NB_BLOCKS = MMA_N / 128;             // 128-row scale blocks of B per stage
     constexpr uint32_t A_BYTES = BM * 128;
@@ -251,6 +252,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
         // ------------------------------------------------------------------ epilogue warps 2..5
         const int q = warp & 3;                      // TMEM lane quadrant this warp may access
         uint32_t tile_it = 0;
+        GatherCtx gc;
+        if constexpr (GATHER) {
+            gc.maps = gmaps.m;
+            gc.n = p.gather.n;
+            gc.stage_smem = smem0 + STAGES * STAGE_BYTES + (uint32_t)(warp - 2) * (GATHER_BOXES * 4096u);
+#ifdef NVFP4_PROFILE
+            gc.mask = p.gather.mask;
+#endif
+            gc.stage = reinterpret_cast<uint4*>(smem_raw + (gc.stage_smem - smem_u32(smem_raw)));
+            gc.uses = 0;
+        }
         for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, tile_it++) {
             const TileInfo ti = locate<BN, DUAL, GROUPED>(t, p, &tmap_a, &tmap_b, &tmap_b2);
             const int row = ti.m0 + q * 32 + lane;
@@ -264,13 +276,12 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             const uint32_t t_lane = tmem_base + buf * ACC1_OFF + ((uint32_t)(q * 32) << 16);
             const int srow = row < ti.M ? row : 0;
             const int wrow0 = ti.m0 + q * 32;          // first row of this warp
-            __half* crow = GATHER ? p.gather.c0 + ((size_t)ti.l * ti.M + wrow0) * p.gather.ldc + p.gather.col0 + n0
-                                  : ti.c + (size_t)srow * ti.N + n0;
-            GatherCtx gc;
-            if (GATHER) {
-                gc.g = &p.gather;
-                gc.stage = reinterpret_cast<uint4*>(smem_raw + (smem0 - smem_u32(smem_raw)) + STAGES * STAGE_BYTES) + (warp - 2) * 256;
-                gc.rows = min(32, ti.M - wrow0);
+            __half* crow = GATHER ? nullptr : ti.c + (size_t)srow * ti.N + n0;
+            if constexpr (GATHER) {
+                gc.x = p.gather.col0 + n0;
+                gc.y = wrow0;
+                gc.z = ti.l;
+                gc.rows_exist = wrow0 < ti.M;
             }
             QuantOut qo;
             if (QOUT) {
@@ -289,6 +300,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+        }
+        // the boxes stay in this CTA's shared memory until the last bulk store has read them, and the kernel's
+        // results are complete only when the stores are
+        if constexpr (GATHER) {
+            if (lane < gc.n) tma_store_wait_all<0>();
         }
     }
 
@@ -356,11 +372,11 @@ int make_scale_tmap(CUtensorMap* map, const void* base, long atoms) {
 
 template <int BN, bool DUAL, bool GROUPED, int STAGES, bool QOUT = false, bool GATHER = false>
 static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const typename GatherMapsOf<GATHER>::type& gm = {}) {
     constexpr int MMA_N = DUAL ? 2 * BN : BN;
     constexpr size_t STAGE = 128 * 128 + MMA_N * 128 + 2048 + (MMA_N / 128) * 2048;
-    // + slack for the 1024-byte alignment (+ 4 KB per epilogue warp to turn chunks for the gathering stores)
-    constexpr size_t SMEM = STAGES * STAGE + 1024 + (GATHER ? 4 * 4096 : 0);
+    // + slack for the 1024-byte alignment (+ the 4 KB boxes of the epilogue warps for the gathering stores)
+    constexpr size_t SMEM = STAGES * STAGE + 1024 + (GATHER ? 4 * GATHER_BOXES * 4096 : 0);
     static_assert(SMEM <= 227 * 1024 - 256, "shared memory");
     auto kern = gemm_kernel<BN, DUAL, GROUPED, STAGES, QOUT, GATHER>;
     static bool configured[64] = {};
@@ -375,7 +391,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const CUten
     }
     if (p.total_tiles <= 0) return NVFP4_OK;
     const int grid = p.total_tiles < sm_count(dev) ? p.total_tiles : sm_count(dev);
-    kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, p);
+    kern<<<grid, GEMM_THREADS, SMEM, stream>>>(ta, tb, tb2, gm, p);
     e = cudaGetLastError();
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
@@ -496,16 +512,50 @@ extern "C" int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* 
     return launch_gemm<128, true, false, 4, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
 }
 
-// Fills the gather description of a launch from the ranks' buffer addresses.
-static int fill_gather(GatherOut& g, void* const* c_all, int world, int rank, int N_local) {
+// Tensor map over one rank's full C, [L][M][ldc] fp16: box 64 columns x 32 rows (one epilogue warp's rows, 128
+// bytes of each), 128-byte swizzle; rows past M are clipped by the store.  Kept per thread like the operand maps.
+static int make_output_tmap(CUtensorMap* map, const void* base, int M, int ldc, int L) {
+    struct Entry { const void* base; int M, ldc, L; CUtensorMap m; bool valid; };
+    constexpr int WAYS = 16;
+    thread_local Entry cache[WAYS] = {};
+    thread_local int victim = 0;
+    for (int i = 0; i < WAYS; i++) {
+        const Entry& e = cache[i];
+        if (e.valid && e.base == base && e.M == M && e.ldc == ldc && e.L == L) {
+            *map = e.m;
+            return NVFP4_OK;
+        }
+    }
+    const uint64_t dims[3] = {(uint64_t)ldc, (uint64_t)M, (uint64_t)L};
+    const uint64_t strides[2] = {(uint64_t)ldc * 2u, (uint64_t)M * (uint64_t)ldc * 2u};
+    const uint32_t box[3] = {64u, 32u, 1u};
+    int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, base, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    cache[victim] = Entry{base, M, ldc, L, *map, true};
+    victim = (victim + 1) % WAYS;
+    return NVFP4_OK;
+}
+
+// Fills the gather description and the ranks' output maps of a launch from the ranks' buffer addresses.
+static int fill_gather(GatherOut& g, GatherMaps& gm, void* const* c_all, int world, int rank, int M, int N_local, int L) {
     if (!c_all) return NVFP4_ERR_NULL;
     if (world < 1 || world > 8 || rank < 0 || rank >= world) return NVFP4_ERR_SHAPE;
-    for (int r = 0; r < world; r++) {
-        if (!c_all[r]) return NVFP4_ERR_NULL;
-        if ((uintptr_t)c_all[r] & 31) return NVFP4_ERR_ALIGN;
-        g.d[r] = (long long)((intptr_t)c_all[r] - (intptr_t)c_all[0]);
+    g.n = world; g.ldc = N_local * world; g.col0 = rank * N_local;
+#ifdef NVFP4_PROFILE
+    {   // timing experiments: "own" = only this rank's copy, "peers" = every copy but this rank's, else a bit mask
+        const char* e_ = getenv("NVFP4_GATHER_MASK");
+        if (e_ && !strcmp(e_, "own")) g.mask = 1u << rank;
+        else if (e_ && !strcmp(e_, "peers")) g.mask = ~(1u << rank);
+        else if (e_) g.mask = (unsigned)strtoul(e_, nullptr, 0);
     }
-    g.n = world; g.ldc = N_local * world; g.col0 = rank * N_local; g.c0 = (__half*)c_all[0];
+#endif
+    for (int r = 0; r < 8; r++) {
+        void* c = c_all[r < world ? r : 0];   // unused entries repeat a valid map
+        if (!c) return NVFP4_ERR_NULL;
+        if ((uintptr_t)c & 31) return NVFP4_ERR_ALIGN;
+        int rc = make_output_tmap(&gm.m[r], c, M, g.ldc, L);
+        if (rc) return rc;
+    }
     return NVFP4_OK;
 }
 
@@ -522,7 +572,8 @@ extern "C" int nvfp4_gemm_allgather(const void* a, const void* b, const void* sf
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     GemmParams p;
-    rc = fill_gather(p.gather, c_all, world, rank, N_local);
+    GatherMaps gm;
+    rc = fill_gather(p.gather, gm, c_all, world, rank, M, N_local, L);
     if (rc) return rc;
     const long tiles256 = (long)((M + 127) / 128) * (N_local / 256) * L;
     const bool wide = (N_local % 256 == 0) && tiles256 >= sm_count(dev);
@@ -537,9 +588,12 @@ extern "C" int nvfp4_gemm_allgather(const void* a, const void* b, const void* sf
     p.budget_ns = wait_budget_ns();
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N_local / (wide ? 256 : 128)) * L;
-    // one stage less than the plain kernels: the room goes to the epilogue warps' store staging
-    if (wide) return launch_gemm<256, false, false, 3, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
-    return launch_gemm<128, false, false, 5, false, true>(ta, tb, tb, p, (cudaStream_t)stream);
+#ifdef NVFP4_PROFILE
+    { const char* e_ = getenv("NVFP4_PROF_PTR"); p.prof = e_ ? (unsigned long long*)strtoull(e_, nullptr, 0) : nullptr; }
+#endif
+    // one stage less than the plain kernels: the room goes to the epilogue warps' store boxes
+    if (wide) return launch_gemm<256, false, false, 3, false, true>(ta, tb, tb, p, (cudaStream_t)stream, gm);
+    return launch_gemm<128, false, false, (GATHER_BOXES <= 2 ? 5 : 4), false, true>(ta, tb, tb, p, (cudaStream_t)stream, gm);
 }
 
 extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const void* b2, const void* sfa_sw,
@@ -554,7 +608,8 @@ extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const vo
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     GemmParams p;
-    rc = fill_gather(p.gather, c_all, world, rank, N_local);
+    GatherMaps gm;
+    rc = fill_gather(p.gather, gm, c_all, world, rank, M, N_local, L);
     if (rc) return rc;
     CUtensorMap ta, tb1, tb2;
     rc = make_operand_tmap(&ta, a, M, K, L, 128);
@@ -569,7 +624,7 @@ extern "C" int nvfp4_dual_gemm_allgather(const void* a, const void* b1, const vo
     p.budget_ns = wait_budget_ns();
     p.table = nullptr; p.G = 0;
     p.total_tiles = ((M + BM - 1) / BM) * (N_local / 128) * L;
-    return launch_gemm<128, true, false, 3, false, true>(ta, tb1, tb2, p, (cudaStream_t)stream);
+    return launch_gemm<128, true, false, 3, false, true>(ta, tb1, tb2, p, (cudaStream_t)stream, gm);
 }
 
 // ------------------------------------------------------------------------------------------ grouped GEMM
