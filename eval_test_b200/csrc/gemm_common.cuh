@@ -40,7 +40,10 @@ struct alignas(64) PairGroupEntry {
 
 // Fused all-gather of an N-sharded GEMM: every output tile is stored into the full C buffer of every rank (peer
 // memory mapped into this process) by asynchronous bulk tensor stores out of shared memory, one per rank, so that
-// the warps that drain the accumulators do not wait for NVLink.
+// the warps that drain the accumulators do not wait for NVLink (8192^3 on 2 GPUs: 154 us per step against 175 us with
+// plain stores issued by those warps).  What is left is in the memory system: while a tile's stores are on their way
+// the operand loads of the same SM arrive later (the MMA issuer waits twice as long for its stages); four separate
+// sending warps with plain stores behaved the same, and so did pacing them.
 #ifndef NVFP4_GATHER_BOXES
 #define NVFP4_GATHER_BOXES 2
 #endif

@@ -77,8 +77,8 @@ int nvfp4_dual_gemm_nvfp4(const void* a, const void* b1, const void* b2, const v
 /* N-sharded GEMM / dual GEMM with the all-gather of the output fused into the epilogue: this rank computes the
  * columns [rank*N_local, (rank+1)*N_local) of C and stores every piece of them into the full C buffer
  * [L][M][N_local*world] of EVERY rank: c_all[r] is rank r's buffer as mapped into this process (peer memory:
- * symmetric memory or an IPC mapping; c_all[rank] is the local one), 32-byte aligned; world <= 8.  Plain stores over
- * NVLink, no collective call.  The caller provides two orderings across ranks: "all ranks have finished" (a
+ * symmetric memory or an IPC mapping; c_all[rank] is the local one), 32-byte aligned; world <= 8.  Asynchronous bulk
+ * tensor stores (TMA stores, no multicast) out of shared memory over NVLink, no collective call.  The caller provides two orderings across ranks: "all ranks have finished" (a
  * barrier on the stream) before C is read, and "all ranks' readers have finished" (a second barrier, or a second
  * buffer used in alternation) before the next call into the same buffers - a rank that has passed the first
  * barrier would otherwise overwrite a copy that a peer is still reading.
