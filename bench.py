@@ -359,7 +359,8 @@ class DualGemmNvfp4Workload(DualGemmWorkload):
 class GroupedGemmWorkload:
     """MoE expert layer: 64 groups, N = 4096, K = 7168, M_g ~ Poisson(128) clipped to [0, 1024] from
     numpy.random.default_rng(0).  At this M the layer is HBM-bound (every weight byte is read once), so the
-    metric is algorithmic GB/s.  N > 1: groups are dealt round-robin to the ranks (strong scaling)."""
+    metric is algorithmic GB/s.  N > 1: the groups are dealt to the ranks by shard.assign_groups, balanced by weight
+    bytes (strong scaling)."""
     name = "grouped_gemm_g64_n4096_k7168_poisson128"
     metric = "nvfp4_grouped_gemm_hbm_gbs"
     unit, per = "GB/s", 1e9
