@@ -717,6 +717,7 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     if (G > 65536) return NVFP4_ERR_TOO_MANY_GROUPS;
     bool wide = true;
     int live = 0;
+    long tiles256 = 0;
     for (int g = 0; g < G; g++) {
         const nvfp4_group_t& q = groups[g];
         if (q.M < 0 || q.N <= 0 || q.K <= 0) return NVFP4_ERR_SHAPE;
@@ -730,6 +731,7 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
         }
         if ((uintptr_t)q.c & 31) return NVFP4_ERR_ALIGN;
         if (q.N % 256 != 0) wide = false;
+        tiles256 += (long)((q.M + BM - 1) / BM) * (q.N / 256);
         live++;
     }
     if (live == 0) return NVFP4_OK;
@@ -737,6 +739,9 @@ extern "C" int nvfp4_grouped_gemm(const nvfp4_group_t* groups, int G, float alph
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
+    // 256-wide tiles only when they still fill the machine, as for the plain GEMM (two groups of 3072 or 4096 columns:
+    // 60 - 64 wide tiles for 148 SMs; 128-wide ones took 9.7 against 13.0 us and 7.4 against 9.4 us)
+    if (tiles256 < sm_count(dev)) wide = false;
     // CTA pairs (256 x 256 tiles, gemm_pair_kernel<false, true>) are opt-in here (NVFP4_GEMM_PAIR=1): on the expert
     // layer of 64 groups with M_g around 128 they measured 234.7 us against 214.2 us for the single-CTA kernel.  The
     // layer streams its weights from HBM; a pair advances only when BOTH CTAs' halves of a stage have arrived, and
