@@ -312,7 +312,7 @@ print("splitk ok")
 @pytest.mark.parametrize("cluster", [2, 4, 8])
 def test_gemm_cluster_split_k_in_a_child_process(cluster):
     """The cluster split-K kernel with every cluster size (forced through NVFP4_GEMM_SPLITK, read once per
-    process): dyadic inputs must match the oracle bit for bit (the partial sums and their rank-ordered reduction
+    process): dyadic inputs must match the oracle bit for bit (the partial sums and their fixed-order reduction
     are exact), including an uneven split of the K steps (7 or 10 steps), ragged M and batches; a quantised case
     within the harness's tolerance."""
     import os
