@@ -54,3 +54,22 @@ def test_shims_reject_wrong_layouts():
         _args.operand_ptr(t, 128, 64, 1, "a")
     with pytest.raises(ValueError, match="shape"):
         _args.operand_ptr(t, 256, 64, 1, "a")
+
+
+def test_another_build_can_be_loaded_by_environment_variable(tmp_path):
+    """NVFP4_B200_LIB names the library file that load() opens (an instrumented build, say); build() keeps writing
+    the one next to the package."""
+    import os
+    import shutil
+    import subprocess
+    import sys
+    from eval_test_b200 import _lib
+    other = tmp_path / "libother.so"
+    shutil.copy(_lib.BUILT_SO, other)
+    code = ("from eval_test_b200 import _lib; lib = _lib.load(); "
+            "print(_lib.SO_PATH, _lib.BUILT_SO, lib.nvfp4_abi_version())")
+    out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, NVFP4_B200_LIB=str(other)),
+                         cwd=str(Path(__file__).resolve().parent.parent), capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    loaded, built, version = out.stdout.split()
+    assert loaded == str(other.resolve()) and built == str(_lib.BUILT_SO) and int(version) >= 1
