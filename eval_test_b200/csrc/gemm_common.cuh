@@ -426,5 +426,8 @@ int max_pairs_grouped(int dev);
 // size (2, 4, 8) or 0 when the persistent kernel should be used; maps with 128-row boxes.
 int splitk_factor(int M, int N, int K, int L, int dev);
 int launch_gemm_splitk(int S, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream);
+// The dual GEMM on the same kernel, S = 2 or 4 (both products are reduced across the cluster before silu(x) * y).
+int launch_dual_gemm_splitk(int S, const CUtensorMap& ta, const CUtensorMap& tb1, const CUtensorMap& tb2, const GemmParams& p,
+                            cudaStream_t stream);
 
 }  // namespace nvfp4

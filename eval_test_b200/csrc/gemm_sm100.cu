@@ -482,6 +482,15 @@ extern "C" int nvfp4_dual_gemm(const void* a, const void* b1, const void* b2, co
     static const int pair_mode = [] { const char* e_ = getenv("NVFP4_GEMM_PAIR"); return e_ ? atoi(e_) : 2; }();
     if (pair_mode != 0 && M >= 256 && (pair_mode == 1 || pair_kernel_suits(M, N, K, L, true, dev)))
         return launch_gemm_pair(true, ta, tb1, tb2, p, (cudaStream_t)stream);
+    // few tiles and a long K loop: split K across a cluster of 2 or 4, as for the GEMM (a CTA streams its operands
+    // at what its shared memory holds in flight divided by the load latency, so the SMs that would idle are worth
+    // more than the reduction costs); NVFP4_GEMM_SPLITK = 0 turns it off, 2 or 4 forces that size where it fits
+    static const int splitk_mode = [] { const char* e_ = getenv("NVFP4_GEMM_SPLITK"); return e_ ? atoi(e_) : -1; }();
+    int split = splitk_mode != 0 ? splitk_factor(M, N, K, L, dev) : 0;
+    if ((splitk_mode == 2 || splitk_mode == 4) && (long)p.total_tiles * splitk_mode <= 2 * sm_count(dev) &&
+        K / BK >= splitk_mode)
+        split = splitk_mode;
+    if (split) return launch_dual_gemm_splitk(split, ta, tb1, tb2, p, (cudaStream_t)stream);
     return launch_gemm<128, true, false, 4>(ta, tb1, tb2, p, (cudaStream_t)stream);
 }
 

@@ -27,17 +27,18 @@
 
 namespace nvfp4 {
 
-constexpr int SK_BN = 128;
-// six stages of 36 KB: with a cold L2 (how the harness times a call) M=128 N=7168 K=16384 takes 21.3 us against
-// 23.8 us with four stages
-constexpr int SK_STAGES = 6;
+constexpr int SK_BN = 128;   // output columns per tile; the dual GEMM's MMA is 256 wide over [B1; B2]
+// GEMM: six stages of 36 KB (with a cold L2 - how the harness times a call - M=128 N=7168 K=16384 takes 21.3 us
+// against 23.8 us with four stages); dual GEMM: four stages of 54 KB
+__host__ __device__ constexpr int sk_stages(bool dual) { return dual ? 4 : 6; }
 constexpr uint32_t SK_A_BYTES = 128 * 128, SK_B_BYTES = 128 * 128, SK_SF_BYTES = 2048;
-constexpr uint32_t SK_STAGE_BYTES = SK_A_BYTES + SK_B_BYTES + 2 * SK_SF_BYTES;
-constexpr uint32_t SK_RED_BYTES = 128 * SK_BN * 4;   // fp32 partial tile
+__host__ __device__ constexpr uint32_t sk_stage_bytes(bool dual) { return SK_A_BYTES + (dual ? 2 : 1) * (SK_B_BYTES + SK_SF_BYTES) + SK_SF_BYTES; }
+__host__ __device__ constexpr uint32_t sk_red_bytes(bool dual) { return 128 * SK_BN * 4 * (dual ? 2 : 1); }   // fp32 partial tile
 // the partial tile reuses the stage ring: once "accumulator complete" has fired, every load has landed and every
 // MMA has read its stage
-static_assert(SK_STAGES * SK_STAGE_BYTES >= SK_RED_BYTES, "the partial tile lives in the stage ring");
-constexpr size_t SK_SMEM = SK_STAGES * SK_STAGE_BYTES + 1024;
+static_assert(sk_stages(false) * sk_stage_bytes(false) >= sk_red_bytes(false) &&
+              sk_stages(true) * sk_stage_bytes(true) >= sk_red_bytes(true), "the partial tile lives in the stage ring");
+__host__ __device__ constexpr size_t sk_smem(bool dual) { return sk_stages(dual) * sk_stage_bytes(dual) + 1024; }
 
 __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
     float4 v;
@@ -48,15 +49,20 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t cluster_addr) {
     return v;
 }
 
-template <int S>
+template <int S, bool DUAL>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                   const GemmParams p) {
-    constexpr int STAGES = SK_STAGES;
-    constexpr uint32_t TCOLS = 256;                    // accumulator 128 columns + scales 2 x 32
-    constexpr uint32_t SF_BASE = 128;
+                   const __grid_constant__ CUtensorMap tmap_b2, const GemmParams p) {
+    constexpr int STAGES = sk_stages(DUAL);
+    constexpr uint32_t SK_STAGE_BYTES = sk_stage_bytes(DUAL);
+    constexpr int MMA_N = DUAL ? 2 * SK_BN : SK_BN;    // accumulator columns: x = A.B1 in 0..127, y = A.B2 in 128..255
+    constexpr uint32_t SF_COLS = 16 + 4 * (MMA_N / 32);   // TMEM columns of one stage's scales
+    constexpr uint32_t SF_BASE = MMA_N;
+    constexpr uint32_t TCOLS = DUAL ? 512 : 256;       // accumulator + two alternating scale regions, a power of two
+    static_assert(SF_BASE + 2 * SF_COLS <= TCOLS, "tensor memory");
     constexpr int SLICE = SK_BN / S;                   // output columns this CTA reduces
     static_assert(S == 2 || S == 4 || S == 8, "cluster size");
+    static_assert(!DUAL || SLICE >= 32, "dual GEMM: whole 32-column chunks per CTA");
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 2];
@@ -73,6 +79,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     if (threadIdx.x == 0) {
         prefetch_tmap(&tmap_a);
         prefetch_tmap(&tmap_b);
+        if (DUAL) prefetch_tmap(&tmap_b2);
         for (int s = 0; s < STAGES; s++) {
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
@@ -115,6 +122,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
     const size_t sf_row_block = (size_t)(p.K / 64) * 512;
     const uint8_t* sfa_t = p.sfa + ((size_t)l * tiles_m + mt) * sf_row_block;
     const uint8_t* sfb_t = p.sfb + ((size_t)l * tiles_n + nt) * sf_row_block;
+    const uint8_t* sfb2_t = DUAL ? p.sfb2 + ((size_t)l * tiles_n + nt) * sf_row_block : nullptr;
 
     if (warp == 0) {
         if (elect_one()) {
@@ -126,14 +134,16 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 }
                 const uint32_t full = full0 + 8 * slot;
                 const uint32_t sA = smem0 + slot * SK_STAGE_BYTES, sB = sA + SK_A_BYTES;
-                const uint32_t sSFA = sB + SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
+                const uint32_t sSFA = sB + (DUAL ? 2 : 1) * SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
                 const int k0 = (kfirst + it) * BK;
                 mbar_arrive_expect_tx(full, SK_STAGE_BYTES);
                 tma_load_3d(sA, &tmap_a, k0, m0, l, full);
                 tma_load_3d(sB, &tmap_b, k0, n0, l, full);
+                if (DUAL) tma_load_3d(sB + SK_B_BYTES, &tmap_b2, k0, n0, l, full);
                 const size_t koff = (size_t)(k0 / 64) * 512;
                 bulk_g2s(sSFA, sfa_t + koff, 2048u, full);
                 bulk_g2s(sSFB, sfb_t + koff, 2048u, full);
+                if (DUAL) bulk_g2s(sSFB + 2048u, sfb2_t + koff, 2048u, full);
             }
         }
         __syncwarp();
@@ -141,7 +151,7 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         cluster_wait_acquire();
     } else if (warp == 1) {
         if (elect_one()) {
-            constexpr uint32_t idesc = make_idesc_nvfp4(BM, SK_BN);
+            constexpr uint32_t idesc = make_idesc_nvfp4(BM, MMA_N);
             bool alive = true;
             for (int it = 0; it < kcount; it++) {
                 const int slot = it % STAGES;
@@ -152,17 +162,19 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
                 }
                 tc_fence_after_sync();
                 const uint32_t sA = smem0 + slot * SK_STAGE_BYTES, sB = sA + SK_A_BYTES;
-                const uint32_t sSFA = sB + SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
-                const uint32_t t_sfa = tmem_base + SF_BASE + (it & 1) * 32, t_sfb = t_sfa + 16;
+                const uint32_t sSFA = sB + (DUAL ? 2 : 1) * SK_B_BYTES, sSFB = sSFA + SK_SF_BYTES;
+                const uint32_t t_sfa = tmem_base + SF_BASE + (it & 1) * SF_COLS, t_sfb = t_sfa + 16;
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++) {
                     tc_cp_sf_atom(t_sfa + 4 * ks, make_desc_sf(sSFA + 512 * ks));
-                    tc_cp_sf_atom(t_sfb + 4 * ks, make_desc_sf(sSFB + 512 * ks));
+#pragma unroll
+                    for (int j = 0; j < MMA_N / 128; j++)
+                        tc_cp_sf_atom(t_sfb + ks * (MMA_N / 32) + 4 * j, make_desc_sf(sSFB + j * 2048 + 512 * ks));
                 }
 #pragma unroll
                 for (int ks = 0; ks < 4; ks++)
                     tc_mma_nvfp4(tmem_base, make_desc_k_sw128(sA + 32 * ks), make_desc_k_sw128(sB + 32 * ks), idesc,
-                                 t_sfa + 4 * ks, t_sfb + 4 * ks, (it | ks) != 0 ? 1u : 0u);
+                                 t_sfa + 4 * ks, t_sfb + ks * (MMA_N / 32), (it | ks) != 0 ? 1u : 0u);
                 tc_commit(empty0 + 8 * slot);
             }
             if (alive) tc_commit(acc_full);
@@ -184,9 +196,9 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             // consecutive addresses, for the writes here and for the peers' reads below
             uint8_t* red_local = smem_raw + (red0 - smem_u32(smem_raw));
 #pragma unroll
-            for (int cc = 0; cc < SK_BN / 32; cc++) {
-                // a chunk that holds nothing but this CTA's own slice stays in tensor memory
-                if (SLICE >= 32 && cc >= own_chunk0 && cc < own_chunk0 + OWN_CHUNKS) continue;
+            for (int cc = 0; cc < MMA_N / 32; cc++) {
+                // a chunk that holds nothing but this CTA's own slice (of x or of y) stays in tensor memory
+                if (SLICE >= 32 && (cc & 3) >= own_chunk0 && (cc & 3) < own_chunk0 + OWN_CHUNKS) continue;
                 uint32_t v[32];
                 tc_ld_32x32(t_lane + cc * 32, v);
                 tc_wait_ld();
@@ -202,18 +214,21 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
         cluster_wait_acquire();     // the peers' barriers exist
         __syncwarp();
         if (lane < S && lane != (int)rank) mbar_arrive_cluster(mapa_shared(red_ready, (uint32_t)lane));
-        float acc[SLICE];
+        constexpr int HALVES = DUAL ? 2 : 1;        // dual GEMM: the slice of x, then the same slice of y
+        float acc[HALVES * SLICE];
         if (ok) {
             // this CTA's own slice, while the peers' signals are on their way
             if constexpr (SLICE >= 32) {
 #pragma unroll
-                for (int i = 0; i < OWN_CHUNKS; i++) {
-                    uint32_t v[32];
-                    tc_ld_32x32(t_lane + (own_chunk0 + i) * 32, v);
-                    tc_wait_ld();
+                for (int h = 0; h < HALVES; h++)
 #pragma unroll
-                    for (int j = 0; j < 32; j++) acc[32 * i + j] = __uint_as_float(v[j]);
-                }
+                    for (int i = 0; i < OWN_CHUNKS; i++) {
+                        uint32_t v[32];
+                        tc_ld_32x32(t_lane + (h * 4 + own_chunk0 + i) * 32, v);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int j = 0; j < 32; j++) acc[h * SLICE + 32 * i + j] = __uint_as_float(v[j]);
+                    }
             } else {
                 uint32_t v[32];
                 tc_ld_32x32(t_lane + own_chunk0 * 32, v);
@@ -237,18 +252,26 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
             for (int i = 1; i < S; i++) {
                 const uint32_t peer = mapa_shared(red0, (rank + (uint32_t)i) % (uint32_t)S);
 #pragma unroll
-                for (int j = 0; j < SLICE / 4; j++) {
-                    const int c4 = (int)rank * (SLICE / 4) + j;
-                    const float4 v = ld_cluster_f4(peer + (uint32_t)((c4 * 128 + row_in_tile) * 16));
-                    acc[4 * j] += v.x; acc[4 * j + 1] += v.y; acc[4 * j + 2] += v.z; acc[4 * j + 3] += v.w;
-                }
+                for (int h = 0; h < HALVES; h++)
+#pragma unroll
+                    for (int j = 0; j < SLICE / 4; j++) {
+                        const int c4 = h * (SK_BN / 4) + (int)rank * (SLICE / 4) + j;
+                        const float4 v = ld_cluster_f4(peer + (uint32_t)((c4 * 128 + row_in_tile) * 16));
+                        float* a4 = acc + h * SLICE + 4 * j;
+                        a4[0] += v.x; a4[1] += v.y; a4[2] += v.z; a4[3] += v.w;
+                    }
             }
             if (row < p.M) {
                 __half* dst = p.c + ((size_t)l * p.M + row) * p.N + n0 + (int)rank * SLICE;
                 uint32_t o[SLICE / 2];
 #pragma unroll
                 for (int i = 0; i < SLICE / 2; i++) {
-                    __half2 h = __floats2half2_rn(p.alpha * acc[2 * i], p.alpha * acc[2 * i + 1]);
+                    float r0 = p.alpha * acc[2 * i], r1 = p.alpha * acc[2 * i + 1];
+                    if (DUAL) {
+                        r0 = silu_mul(r0, p.alpha * acc[(HALVES - 1) * SLICE + 2 * i]);
+                        r1 = silu_mul(r1, p.alpha * acc[(HALVES - 1) * SLICE + 2 * i + 1]);
+                    }
+                    __half2 h = __floats2half2_rn(r0, r1);
                     o[i] = *reinterpret_cast<uint32_t*>(&h);
                 }
 #pragma unroll
@@ -273,29 +296,31 @@ gemm_splitk_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_cons
 // ------------------------------------------------------------------------------------------ host side
 namespace {
 
-template <int S>
-int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int tiles, cudaStream_t stream) {
+template <int S, bool DUAL>
+int launch_splitk(const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, const GemmParams& p, int tiles,
+                  cudaStream_t stream) {
     static bool done[64] = {};
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return (int)e;
     if (dev >= 64) return NVFP4_ERR_UNSUPPORTED;
     if (!done[dev]) {
-        e = cudaFuncSetAttribute(gemm_splitk_kernel<S>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SK_SMEM);
+        e = cudaFuncSetAttribute(gemm_splitk_kernel<S, DUAL>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)sk_smem(DUAL));
         if (e != cudaSuccess) return (int)e;
         done[dev] = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(tiles * S);
     cfg.blockDim = dim3(GEMM_THREADS);
-    cfg.dynamicSmemBytes = SK_SMEM;
+    cfg.dynamicSmemBytes = sk_smem(DUAL);
     cfg.stream = stream;
     cudaLaunchAttribute attr;
     attr.id = cudaLaunchAttributeClusterDimension;
     attr.val.clusterDim.x = S; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
     cfg.attrs = &attr;
     cfg.numAttrs = 1;
-    e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<S>, ta, tb, p);
+    e = cudaLaunchKernelEx(&cfg, gemm_splitk_kernel<S, DUAL>, ta, tb, tb2, p);
     return e == cudaSuccess ? NVFP4_OK : (int)e;
 }
 
@@ -321,9 +346,20 @@ int splitk_factor(int M, int N, int K, int L, int dev) {
 int launch_gemm_splitk(int S, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, cudaStream_t stream) {
     const int tiles = ((p.M + BM - 1) / BM) * (p.N / SK_BN) * p.L;
     switch (S) {
-        case 2: return launch_splitk<2>(ta, tb, p, tiles, stream);
-        case 4: return launch_splitk<4>(ta, tb, p, tiles, stream);
-        case 8: return launch_splitk<8>(ta, tb, p, tiles, stream);
+        case 2: return launch_splitk<2, false>(ta, tb, tb, p, tiles, stream);
+        case 4: return launch_splitk<4, false>(ta, tb, tb, p, tiles, stream);
+        case 8: return launch_splitk<8, false>(ta, tb, tb, p, tiles, stream);
+        default: return NVFP4_ERR_INTERNAL;
+    }
+}
+
+// The dual GEMM on the same kernel (S = 2 or 4): both products are reduced across the cluster before silu(x) * y.
+int launch_dual_gemm_splitk(int S, const CUtensorMap& ta, const CUtensorMap& tb1, const CUtensorMap& tb2, const GemmParams& p,
+                            cudaStream_t stream) {
+    const int tiles = ((p.M + BM - 1) / BM) * (p.N / SK_BN) * p.L;
+    switch (S) {
+        case 2: return launch_splitk<2, true>(ta, tb1, tb2, p, tiles, stream);
+        case 4: return launch_splitk<4, true>(ta, tb1, tb2, p, tiles, stream);
         default: return NVFP4_ERR_INTERNAL;
     }
 }

@@ -326,6 +326,54 @@ def test_gemm_cluster_split_k_in_a_child_process(cluster):
     assert res.returncode == 0 and "splitk ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
 
 
+_DUAL_SPLITK_CHILD = r'''
+import sys
+import numpy as np, torch
+sys.path.insert(0, sys.argv[1]); sys.path.insert(0, sys.argv[1] + "/tests")
+from _util import dual_oracle_args, out_np, to_device
+from eval_test_b200 import _lib, check, inputs, nvfp4_dual_gemm
+from oracle import nvfp4_oracle as O
+cases = [("ref", 128, 512, 7168, 1), ("ref", 200, 256, 2560, 2), ("quant", 256, 384, 4096, 1), ("quant", 100, 128, 1792, 1)]
+for kind, m, n, k, l in cases:
+    gen = inputs.dual_gemm_reference_style if kind == "ref" else inputs.dual_gemm_quantized
+    d = to_device(gen(m, n, k, l, seed=5, device="cpu"))
+    nvfp4_dual_gemm.custom_kernel(d)
+    torch.cuda.synchronize()
+    assert _lib.device_status(0) == 0
+    got, want = torch.from_numpy(out_np(d[-1])), torch.from_numpy(O.c_dual_gemm(*dual_oracle_args(d)))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == [], (kind, m, n, k, l)
+    assert check.max_delta_ok(got, want)[0], (kind, m, n, k, l)
+print("dual splitk ok")
+'''
+
+
+@pytest.mark.parametrize("cluster", [2, 4])
+def test_dual_gemm_cluster_split_k_in_a_child_process(cluster):
+    """The dual GEMM on the cluster split-K kernel (both products reduced across the cluster before silu(x) * y),
+    cluster sizes 2 and 4 forced through NVFP4_GEMM_SPLITK: reference-style and N(0,1)-quantised inputs, ragged M, an
+    uneven split of the K steps (7 or 10 steps) and batches, against the oracle under the harness's tolerance."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, NVFP4_GEMM_SPLITK=str(cluster))
+    res = subprocess.run([sys.executable, "-c", _DUAL_SPLITK_CHILD, root], env=env, capture_output=True, text=True,
+                         timeout=300)
+    assert res.returncode == 0 and "dual splitk ok" in res.stdout, res.stdout[-2000:] + res.stderr[-2000:]
+
+
+def test_dual_gemm_few_tiles_take_split_k_by_default(oracle):
+    """M = 256, N = 4096, K = 7168 (a benchmark shape of the reference's dual-GEMM list): 64 tiles for 148 SMs, split
+    across clusters of 2 by the default heuristic."""
+    from eval_test_b200 import check, inputs
+    data = to_device(inputs.dual_gemm_reference_style(256, 4096, 7168, 1, seed=1111, device="cpu"))
+    got = torch.from_numpy(_dual(data))
+    want = torch.from_numpy(oracle.c_dual_gemm(*dual_oracle_args(data)))
+    assert check.verbose_allclose(got, want, rtol=1e-3, atol=1e-3) == []
+    assert check.max_delta_ok(got, want)[0]
+
+
 def test_gemm_long_k_takes_split_k_by_default(oracle):
     """M = 128, N = 7168, K = 16384 (the reference's first benchmark shape) is split across clusters of 2 by the
     default heuristic."""
