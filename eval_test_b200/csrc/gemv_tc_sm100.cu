@@ -464,18 +464,9 @@ int launch_tc(const CUtensorMap& ta, const CUtensorMap& tx, const GemvTcParams& 
 
 // Tensor map of A for the one-box-per-stage layout (cached like the operand maps: encoding costs about a microsecond).
 static int make_gemv_a_tmap(CUtensorMap* map, const void* base, int M, int K, int L) {
-    struct Key { const void* base; int M, K, L; };
-    struct Entry { Key k; CUtensorMap m; bool valid; };
-    constexpr int WAYS = 4;
-    thread_local Entry cache[WAYS] = {};
-    thread_local int victim = 0;
-    for (int i = 0; i < WAYS; i++) {
-        const Entry& e = cache[i];
-        if (e.valid && e.k.base == base && e.k.M == M && e.k.K == K && e.k.L == L) {
-            *map = e.m;
-            return NVFP4_OK;
-        }
-    }
+    thread_local TmapCache<> cache = {};
+    const TmapKey key{(uint64_t)(uintptr_t)base, M, K, L, 0};
+    if (cache.find(key, map)) return NVFP4_OK;
     const uint64_t rowb = (uint64_t)(K / 2);
     const uint64_t dims[5] = {256, 8, (uint64_t)(K / BK), (uint64_t)(M / 8), (uint64_t)L};
     const uint64_t strides[4] = {rowb, 128, 8 * rowb, (uint64_t)M * rowb};
@@ -483,11 +474,7 @@ static int make_gemv_a_tmap(CUtensorMap* map, const void* base, int M, int K, in
     int rc = encode_tiled(map, CU_TENSOR_MAP_DATA_TYPE_16U4_ALIGN8B, 5, base, dims, strides, box,
                           CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    Entry& v = cache[victim];
-    victim = (victim + 1) % WAYS;
-    v.k = Key{base, M, K, L};
-    v.m = *map;
-    v.valid = true;
+    cache.put(key, *map);
     return NVFP4_OK;
 }
 

@@ -26,7 +26,7 @@ def compile_kernel():
 import weakref
 
 _CACHE: dict = {}
-_CACHE_MAX = 16
+_CACHE_MAX = 64
 
 
 def _fingerprint(abc_tensors, sf_reordered, problem_sizes):

@@ -143,11 +143,11 @@ def test_grouped_same_call_again_and_from_a_second_stream(oracle):
 
 
 def test_grouped_repeated_calls_and_streams(oracle):
-    """More back-to-back calls than the library has problem-table slots, on two streams: every call's table
-    must stay intact until its launch has read it."""
+    """More distinct problems back to back than the library has problem-table slots (40 for 32), on two streams:
+    every call's table must stay intact until its launch has read it."""
     from eval_test_b200 import inputs, nvfp4_grouped_gemm
     sets = [to_device(inputs.grouped_gemm_reference_style([96 + 8 * i, 128], [128, 256], [256, 512], 2, seed=i,
-                                                          device="cpu")) for i in range(12)]
+                                                          device="cpu")) for i in range(40)]
     streams = [torch.cuda.Stream(), torch.cuda.Stream()]
     torch.cuda.synchronize()
     for rep in range(3):
