@@ -22,8 +22,8 @@ int encode_tiled(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const vo
                  const uint64_t* strides, const uint32_t* box, CUtensorMapSwizzle swizzle);
 
 // Encoding a tensor map costs about a microsecond of host time, which matters for calls whose kernel runs for ten,
-// so the maps a thread has made are kept, direct-mapped on a hash of everything that goes into them.  256 sets: a
-// caller that rotates through dozens of problems (the harness times 50 inputs in turn) still finds its maps.
+// so the maps a thread has made are kept, two-way set-associative on a hash of everything that goes into them.  256
+// sets: a caller that rotates through dozens of problems (the harness times 50 inputs in turn) still finds its maps.
 struct TmapKey {
     uint64_t base;
     int32_t a, b, c, d;   // the dimensions and box sizes the map depends on
@@ -31,7 +31,8 @@ struct TmapKey {
 template <int SETS = 256>
 struct TmapCache {
     struct Entry { TmapKey k; CUtensorMap m; bool valid; };
-    Entry e[SETS];
+    Entry e[SETS][2];          // two ways per set; `old[s]` is the way to replace next
+    unsigned char old[SETS];
     static unsigned slot(const TmapKey& k) {
         uint64_t h = (k.base >> 4) * 0x9E3779B97F4A7C15ull;
         h ^= ((uint64_t)(uint32_t)k.a << 32 | (uint32_t)k.b) * 0xC2B2AE3D27D4EB4Full;
@@ -41,15 +42,23 @@ struct TmapCache {
     static bool same(const TmapKey& x, const TmapKey& y) {
         return x.base == y.base && x.a == y.a && x.b == y.b && x.c == y.c && x.d == y.d;
     }
-    bool find(const TmapKey& k, CUtensorMap* out) const {
-        const Entry& en = e[slot(k)];
-        if (!en.valid || !same(en.k, k)) return false;
-        *out = en.m;
-        return true;
+    bool find(const TmapKey& k, CUtensorMap* out) {
+        const unsigned s = slot(k);
+        for (int w = 0; w < 2; w++) {
+            const Entry& en = e[s][w];
+            if (en.valid && same(en.k, k)) {
+                *out = en.m;
+                old[s] = (unsigned char)(1 - w);
+                return true;
+            }
+        }
+        return false;
     }
     void put(const TmapKey& k, const CUtensorMap& m) {
-        Entry& en = e[slot(k)];
+        const unsigned s = slot(k);
+        Entry& en = e[s][old[s] & 1];
         en.k = k; en.m = m; en.valid = true;
+        old[s] = (unsigned char)(1 - (old[s] & 1));
     }
 };
 
